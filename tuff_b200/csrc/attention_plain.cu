@@ -1,0 +1,220 @@
+// Attention over a paged key/value cache: the plain kernels.
+//
+//   tuff_qk_norm_rope_write   per-head RMSNorm of q and k, NeoX rotation at the
+//                             token's absolute position, rotated K and raw V
+//                             stored in the request's pages
+//                             (reference: src/lfm25_gpu.cu:420-501)
+//   tuff_paged_attention_plain  causal softmax(q.k/sqrt(hd)) v over the cached
+//                             keys 0..p (or the last `window` of them), grouped
+//                             query heads sharing a key/value head
+//                             (reference: src/lfm25_gpu.cu:506-578)
+//
+// The reference keeps one contiguous fp32 cache per sequence and is written for
+// head size 64; here the cache is paged ([page][kv_head][slot][hd], looked up
+// through a block table per batch row), the head size is any value up to 256,
+// and one launch covers a batch that mixes prompt portions and decode tokens.
+// Scores, softmax and the weighted sum are fp32.  Which warp takes which key
+// depends on the key's index alone, so a token's result does not depend on how
+// the batch was cut.
+#include "common.cuh"
+
+namespace {
+constexpr int MAX_HD = 256;
+constexpr int QKV_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(QKV_WARPS * 32)
+qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_w,
+                          const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
+                          const int* __restrict__ positions, const int* __restrict__ row_of_token,
+                          const int* __restrict__ block_table, int max_blocks,
+                          T* __restrict__ k_pages, T* __restrict__ v_pages,
+                          int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv) {
+    __shared__ float sh[QKV_WARPS][MAX_HD];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = positions[t];
+    const int r = row_of_token[t];
+    const int n_heads = H + 2 * G;
+    const int half = rot_dim >> 1;
+    T* base = qkv + (size_t)t * n_heads * hd;
+    size_t page_base = 0;
+    int in_page = 0;
+    if (write_kv) {
+        const int page = block_table[(size_t)r * max_blocks + pos / page_size];
+        in_page = pos % page_size;
+        page_base = (size_t)page * G;
+    }
+    for (int head = warp; head < n_heads; head += QKV_WARPS) {
+        T* x = base + (size_t)head * hd;
+        const bool is_q = head < H, is_k = !is_q && head < H + G;
+        if (!is_q && !is_k) {          // value head: copy to its page
+            if (write_kv) {
+                const int g = head - H - G;
+                T* dst = v_pages + ((page_base + g) * page_size + in_page) * hd;
+                for (int e = lane; e < hd; e += 32) dst[e] = x[e];
+            }
+            continue;
+        }
+        const float* w = is_q ? q_norm_w : k_norm_w;
+        float ss = 0.f;
+        for (int e = lane; e < hd; e += 32) {
+            const float v = to_f32(x[e]);
+            sh[warp][e] = v;
+            ss = fmaf(v, v, ss);
+        }
+        ss = warp_sum(ss);
+        const float scale = w ? rsqrtf(ss / (float)hd + eps) : 1.f;
+        __syncwarp();
+        if (w)
+            for (int e = lane; e < hd; e += 32) sh[warp][e] = sh[warp][e] * scale * w[e];
+        __syncwarp();
+        T* dst = x;
+        if (is_k) {
+            if (!write_kv) dst = nullptr;
+            else dst = k_pages + ((page_base + (head - H)) * page_size + in_page) * hd;
+        }
+        for (int e = lane; e < hd; e += 32) {
+            float v = sh[warp][e];
+            if (e < rot_dim) {
+                const int j = e < half ? e : e - half;
+                float sn, cs;
+                sincosf((float)pos * inv_freq[j], &sn, &cs);
+                v = e < half ? v * cs - sh[warp][e + half] * sn
+                             : sh[warp][e - half] * sn + v * cs;
+            }
+            if (is_q) x[e] = from_f32<T>(v);
+            else {
+                if (dst) dst[e] = from_f32<T>(v);
+                x[e] = from_f32<T>(v);
+            }
+        }
+        __syncwarp();
+    }
+}
+
+constexpr int ATT_WARPS = 4;
+constexpr int MAX_PER_LANE = MAX_HD / 32;
+
+template <typename T>
+__global__ void __launch_bounds__(ATT_WARPS * 32)
+paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
+                             const T* __restrict__ v_pages, const int* __restrict__ block_table,
+                             int max_blocks, const int* __restrict__ positions,
+                             const int* __restrict__ row_of_token, T* __restrict__ out,
+                             int H, int G, int hd, int page_size, float scale, int window) {
+    __shared__ float sh_acc[ATT_WARPS][MAX_HD];
+    __shared__ float sh_m[ATT_WARPS], sh_l[ATT_WARPS];
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = h / (H / G);
+    const int pos = positions[t];
+    const int r = row_of_token[t];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int* bt = block_table + (size_t)r * max_blocks;
+
+    float qv[MAX_PER_LANE], acc[MAX_PER_LANE];
+    const T* qp = q + (size_t)t * q_stride + (size_t)h * hd;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        qv[i] = e < hd ? to_f32(qp[e]) * scale : 0.f;
+        acc[i] = 0.f;
+    }
+    float m = -INFINITY, l = 0.f;
+    for (int j = lo + warp; j <= pos; j += ATT_WARPS) {
+        const int page = bt[j / page_size];
+        const size_t off = (((size_t)page * G + g) * page_size + (j % page_size)) * hd;
+        const T* kp = k_pages + off;
+        const T* vp = v_pages + off;
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < hd) s = fmaf(qv[i], to_f32(kp[e]), s);
+        }
+        s = warp_sum(s);
+        const float m_new = fmaxf(m, s);
+        const float corr = expf(m - m_new);     // exp(-inf) = 0 on the first key
+        const float p = expf(s - m_new);
+        l = l * corr + p;
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < hd) acc[i] = acc[i] * corr + p * to_f32(vp[e]);
+        }
+        m = m_new;
+    }
+    if (lane == 0) { sh_m[warp] = m; sh_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        if (e < hd) sh_acc[warp][e] = acc[i];
+    }
+    __syncthreads();
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) m_all = fmaxf(m_all, sh_m[w]);
+    float l_all = 0.f;
+    float f[ATT_WARPS];
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+        f[w] = sh_l[w] > 0.f ? expf(sh_m[w] - m_all) : 0.f;
+        l_all += sh_l[w] * f[w];
+    }
+    T* op = out + ((size_t)t * H + h) * hd;
+    for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < ATT_WARPS; ++w) o += sh_acc[w][e] * f[w];
+        op[e] = from_f32<T>(o / l_all);
+    }
+}
+}  // namespace
+
+// qkv [n_tokens, (H+2G)*hd] is updated in place: q heads normed and rotated, k
+// heads too (and copied to the pages), v heads copied to the pages.
+// q_norm_w / k_norm_w may be null (no norm); rot_dim = 0 means no rotation;
+// write_kv = 0 leaves the pages alone.
+extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm_w, const float* k_norm_w,
+                                       const float* inv_freq, const int* positions, const int* row_of_token,
+                                       const int* block_table, int max_blocks, void* k_pages, void* v_pages,
+                                       int n_tokens, int H, int G, int hd, int rot_dim, int page_size,
+                                       float eps, int write_kv, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd < 1 || hd > MAX_HD || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || G < 0 || H < 0) return TUFF_E_SIZE;
+    if (write_kv && page_size < 1) return TUFF_E_SIZE;
+    if (dtype == TUFF_F32)
+        qk_norm_rope_write_kernel<float><<<n_tokens, QKV_WARPS * 32, 0, stream>>>(
+            (float*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks,
+            (float*)k_pages, (float*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv);
+    else if (dtype == TUFF_BF16)
+        qk_norm_rope_write_kernel<bf16><<<n_tokens, QKV_WARPS * 32, 0, stream>>>(
+            (bf16*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks,
+            (bf16*)k_pages, (bf16*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv);
+    else
+        return TUFF_E_DTYPE;
+    return launch_status();
+}
+
+// q: [n_tokens, H, hd] with a row stride of q_stride elements; out: [n_tokens, H*hd].
+extern "C" int tuff_paged_attention_plain(const void* q, long long q_stride, const void* k_pages,
+                                          const void* v_pages, int dtype, const int* block_table, int max_blocks,
+                                          const int* positions, const int* row_of_token, void* out,
+                                          int n_tokens, int H, int G, int hd, int page_size, float scale,
+                                          int window, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd < 1 || hd > MAX_HD || G < 1 || H % G != 0 || page_size < 1 || H > 65535) return TUFF_E_SIZE;
+    dim3 grid(n_tokens, H);
+    if (dtype == TUFF_F32)
+        paged_attention_plain_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
+            (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_blocks,
+            positions, row_of_token, (float*)out, H, G, hd, page_size, scale, window);
+    else if (dtype == TUFF_BF16)
+        paged_attention_plain_kernel<bf16><<<grid, ATT_WARPS * 32, 0, stream>>>(
+            (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,
+            positions, row_of_token, (bf16*)out, H, G, hd, page_size, scale, window);
+    else
+        return TUFF_E_DTYPE;
+    return launch_status();
+}

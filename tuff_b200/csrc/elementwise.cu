@@ -1,0 +1,120 @@
+// Row-wise kernels: embedding gather, RMSNorm, SwiGLU activation, dtype cast.
+//
+// What each computes follows the reference's LFM2.5 path:
+//   embedding   x = E[token]                                  (src/lfm25_gpu.cu:725-741)
+//   RMSNorm     y = x * rsqrt(mean(x^2) + eps) * w, statistics in fp32, the weight
+//               multiplies directly                            (src/lfm25_gpu.cu:207-262)
+//   SwiGLU      act = gate / (1 + exp(-gate)) * up             (src/lfm25_gpu.cu:583-618)
+// The kernels themselves are written for bf16/fp32 activations on sm_100a; the
+// reference's are Q8_1/Q4_K kernels for sm_86.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename WT>
+__global__ void embed_kernel(const int* __restrict__ tokens, const WT* __restrict__ table,
+                             float* __restrict__ out, int d, int vocab) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    const bool ok = tok >= 0 && tok < vocab;
+    if (!ok) tok = 0;
+    const WT* row = table + (size_t)tok * d;
+    float* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = ok ? to_f32(row[i]) : 0.f;
+}
+
+extern "C" int tuff_embed(const int* tokens, const void* table, int table_dtype, float* out,
+                          int n_tokens, int d, int vocab, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == TUFF_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, d, vocab);
+    else if (table_dtype == TUFF_BF16)
+        embed_kernel<bf16><<<n_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, d, vocab);
+    else
+        return TUFF_E_DTYPE;
+    return launch_status();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row.  `row_index` (may be null) picks the input row of
+// each output row, which is how the head norms only the rows whose logits are
+// wanted.  The sum of squares is accumulated per thread over a fixed stride and
+// then across the block, so a row's result does not depend on the batch.
+template <typename InT, typename OutT>
+__global__ void rmsnorm_kernel(const InT* __restrict__ x, const float* __restrict__ w,
+                               OutT* __restrict__ out, const int* __restrict__ row_index,
+                               int d, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int src = row_index ? row_index[r] : r;
+    const InT* xr = x + (size_t)src * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = to_f32(xr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = rsqrtf(ss / (float)d + eps);
+    OutT* o = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x)
+        o[i] = from_f32<OutT>(to_f32(xr[i]) * scale * w[i]);
+}
+
+extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* out, int out_dtype,
+                            const int* row_index, int n_rows, int d, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = 256;
+#define LAUNCH(IT, OT) rmsnorm_kernel<IT, OT><<<n_rows, threads, 0, stream>>>( \
+        (const IT*)x, w, (OT*)out, row_index, d, eps)
+    if (x_dtype == TUFF_F32 && out_dtype == TUFF_F32) LAUNCH(float, float);
+    else if (x_dtype == TUFF_F32 && out_dtype == TUFF_BF16) LAUNCH(float, bf16);
+    else if (x_dtype == TUFF_BF16 && out_dtype == TUFF_BF16) LAUNCH(bf16, bf16);
+    else if (x_dtype == TUFF_BF16 && out_dtype == TUFF_F32) LAUNCH(bf16, float);
+    else return TUFF_E_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// gu is [T, 2F]: gate in columns [0,F), up in columns [F,2F).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int F) {
+    const size_t total = (size_t)n_tokens * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / F;
+        const int f = (int)(i - t * F);
+        const float g = to_f32(gu[t * 2 * F + f]);
+        const float u = to_f32(gu[t * 2 * F + F + f]);
+        out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+extern "C" int tuff_swiglu(const void* gu, void* out, int dtype, int n_tokens, int F, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const size_t total = (size_t)n_tokens * F;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == TUFF_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, F);
+    else if (dtype == TUFF_BF16) swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, n_tokens, F);
+    else return TUFF_E_DTYPE;
+    return launch_status();
+}
+
+// --------------------------------------------------------------------- cast
+template <typename A, typename B>
+__global__ void cast_kernel(const A* __restrict__ in, B* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<B>(to_f32(in[i]));
+}
+
+extern "C" int tuff_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (in_dtype == TUFF_F32 && out_dtype == TUFF_BF16) cast_kernel<float, bf16><<<blocks, threads, 0, stream>>>((const float*)in, (bf16*)out, (size_t)n);
+    else if (in_dtype == TUFF_BF16 && out_dtype == TUFF_F32) cast_kernel<bf16, float><<<blocks, threads, 0, stream>>>((const bf16*)in, (float*)out, (size_t)n);
+    else return TUFF_E_DTYPE;
+    return launch_status();
+}

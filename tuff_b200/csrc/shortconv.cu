@@ -1,0 +1,98 @@
+// Gated short convolution over a batch of portions, continuing per-request state.
+//
+// Per channel c and token t of a request (reference: src/lfm25_gpu.cu:287-337 for
+// one token, src/lfm25_gpu.cu:1046-1099 for consecutive tokens):
+//   bcx = [B | C | x]  (three d-wide thirds of the in_proj output, in this order)
+//   u_t = B_t * x_t
+//   y_t = sum_{j=0..K-1} taps[c][j] * u_{t-(K-1)+j}      (tap K-1 meets the current token)
+//   g_t = C_t * y_t
+//   state after t = the last K-1 values of u, oldest first
+// u before the request's first token is zero; u before the first token of this
+// portion comes from the request's state slot.
+//
+// The reference walks a portion sequentially per channel.  Here every (token,
+// channel) is computed independently from the K values of u it needs, so a long
+// portion runs in parallel, and a second kernel rolls the state afterwards (the
+// first one must only read it).  All arithmetic is fp32; the sum runs over the
+// taps in ascending order whatever the portion's length, so cutting a prompt
+// differently changes nothing.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void shortconv_fwd_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
+                                     const float* __restrict__ state, const int* __restrict__ slot_of_row,
+                                     const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
+                                     T* __restrict__ out, int n_tokens, int d, int K) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;
+    if (c >= d) return;
+    const int r = row_of_token[t];
+    const int i = t - cu_q[r];                 // index inside this portion
+    const size_t ld = (size_t)3 * d;
+    const float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+    float y = 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int back = (K - 1) - j;          // how many tokens before t
+        float u;
+        if (i - back >= 0) {
+            const T* p = bcx + (size_t)(t - back) * ld;
+            u = to_f32(p[c]) * to_f32(p[2 * d + c]);
+        } else {
+            u = st[(size_t)((K - 1) + (i - back)) * d + c];
+        }
+        y = fmaf(taps[(size_t)c * K + j], u, y);
+    }
+    out[(size_t)t * d + c] = from_f32<T>(to_f32(bcx[(size_t)t * ld + d + c]) * y);
+}
+
+// New state entry s (0 = oldest) is u at portion index n-(K-1)+s; if that is
+// negative it is the old entry s+n.  Ascending s reads old entries before they
+// are overwritten, since s+n > s.
+template <typename T>
+__global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
+                                       const int* __restrict__ slot_of_row, const int* __restrict__ cu_q,
+                                       int d, int K) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int r = blockIdx.x;
+    if (c >= d) return;
+    const int q0 = cu_q[r], n = cu_q[r + 1] - q0;
+    if (n <= 0) return;
+    const size_t ld = (size_t)3 * d;
+    float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+    for (int s = 0; s < K - 1; ++s) {
+        const int i = n - (K - 1) + s;
+        float u;
+        if (i >= 0) {
+            const T* p = bcx + (size_t)(q0 + i) * ld;
+            u = to_f32(p[c]) * to_f32(p[2 * d + c]);
+        } else {
+            u = st[(size_t)(s + n) * d + c];
+        }
+        st[(size_t)s * d + c] = u;
+    }
+}
+}  // namespace
+
+// bcx [n_tokens, 3d], taps [d, K] fp32, state [n_slots, K-1, d] fp32, out [n_tokens, d].
+extern "C" int tuff_shortconv(const void* bcx, void* out, int dtype, const float* taps, float* state,
+                              const int* slot_of_row, const int* row_of_token, const int* cu_q,
+                              int n_tokens, int n_rows, int d, int K, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_rows <= 0) return 0;
+    if (K < 2) return TUFF_E_SIZE;
+    const int threads = 128;
+    dim3 g1(n_tokens, ceil_div(d, threads)), g2(n_rows, ceil_div(d, threads));
+    if (dtype == TUFF_F32) {
+        shortconv_fwd_kernel<float><<<g1, threads, 0, stream>>>((const float*)bcx, taps, state, slot_of_row,
+                                                                 row_of_token, cu_q, (float*)out, n_tokens, d, K);
+        shortconv_state_kernel<float><<<g2, threads, 0, stream>>>((const float*)bcx, state, slot_of_row, cu_q, d, K);
+    } else if (dtype == TUFF_BF16) {
+        shortconv_fwd_kernel<bf16><<<g1, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row,
+                                                                row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
+        shortconv_state_kernel<bf16><<<g2, threads, 0, stream>>>((const bf16*)bcx, state, slot_of_row, cu_q, d, K);
+    } else {
+        return TUFF_E_DTYPE;
+    }
+    return launch_status();
+}

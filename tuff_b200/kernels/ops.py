@@ -1,0 +1,224 @@
+"""Python faces of the CUDA kernels: each function checks its tensors, then calls
+the `extern "C"` launcher of the same name on the current CUDA stream.
+
+Nothing here computes on the host or through a library: a tensor that is not on
+a CUDA device is refused, and a launcher that cannot be compiled or loaded
+raises (`tuff_b200.kernels.build.KernelBuildError`).
+"""
+from __future__ import annotations
+
+import ctypes
+import struct
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+_ERRORS = {-2: "unsupported combination of element types", -3: "a size outside what the kernel supports",
+           -4: "a pointer or stride that breaks an alignment rule", -5: "scratch memory too small"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"tensors must be float32 or bfloat16, found {t.dtype}")
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("tuff_b200 kernels run on CUDA tensors only; there is no host path")
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status in _ERRORS:
+        raise KernelError(f"{what}: {_ERRORS[status]}")
+    raise KernelError(f"{what}: CUDA error {status} at launch")
+
+
+def _contig(t: torch.Tensor, name: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _i32(t: torch.Tensor | None, name: str) -> None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, found {t.dtype}")
+
+
+# ----------------------------------------------------------------- elementwise
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = table[tokens[t], :] as float32."""
+    _i32(tokens, "tokens")
+    n, d = out.shape
+    assert out.dtype == torch.float32 and table.shape[1] == d and tokens.numel() == n
+    _contig(table, "table"); _contig(out, "out")
+    lib = load_library("elementwise")
+    _check(lib.tuff_embed(_ptr(tokens), _ptr(table), dtype_code(table), _ptr(out), c_int(n), c_int(d),
+                          c_int(table.shape[0]), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            row_index: torch.Tensor | None = None) -> None:
+    """out[r] = x[row_index[r] or r] * rsqrt(mean(x^2) + eps) * weight."""
+    d = x.shape[-1]
+    n = out.shape[0]
+    assert weight.dtype == torch.float32 and weight.numel() == d and out.shape[-1] == d
+    _contig(x, "x"); _contig(out, "out"); _i32(row_index, "row_index")
+    lib = load_library("elementwise")
+    _check(lib.tuff_rmsnorm(_ptr(x), dtype_code(x), _ptr(weight), _ptr(out), dtype_code(out), _ptr(row_index),
+                            c_int(n), c_int(d), c_float(eps), _stream()), "rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :F]) * gate_up[:, F:]."""
+    n, F = out.shape
+    assert gate_up.shape == (n, 2 * F) and gate_up.dtype == out.dtype
+    _contig(gate_up, "gate_up"); _contig(out, "out")
+    lib = load_library("elementwise")
+    _check(lib.tuff_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out), c_int(n), c_int(F), _stream()), "swiglu")
+
+
+def cast(src: torch.Tensor, out: torch.Tensor) -> None:
+    assert src.numel() == out.numel()
+    _contig(src, "src"); _contig(out, "out")
+    lib = load_library("elementwise")
+    _check(lib.tuff_cast(_ptr(src), dtype_code(src), _ptr(out), dtype_code(out), c_longlong(src.numel()), _stream()),
+           "cast")
+
+
+# ------------------------------------------------------------------------ GEMM
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out (=|+=) a @ w.T with fp32 FFMA accumulation; a [M,K], w [N,K], out [M,N]."""
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    lib = load_library("gemm_plain")
+    _check(lib.tuff_gemm_plain(_ptr(a), dtype_code(a), _ptr(w), dtype_code(w), _ptr(out), dtype_code(out),
+                               c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(w.stride(0)),
+                               c_longlong(out.stride(0)), c_int(1 if accumulate else 0), _stream()), "gemm_plain")
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out (=|+=) a @ w.T, by the kernel that suits the element types and the shape."""
+    gemm_plain(a, w, out, accumulate)
+
+
+# ------------------------------------------------------------------ short conv
+def shortconv(bcx: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_of_row: torch.Tensor,
+              row_of_token: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor) -> None:
+    """Gated short convolution of a batch of portions; rolls each row's state slot."""
+    n, d = out.shape
+    K = taps.shape[1]
+    assert bcx.shape == (n, 3 * d) and taps.shape == (d, K) and taps.dtype == torch.float32
+    assert state.dtype == torch.float32 and state.shape[1:] == (K - 1, d) and bcx.dtype == out.dtype
+    for t, nm in ((slot_of_row, "slot_of_row"), (row_of_token, "row_of_token"), (cu_q, "cu_q")):
+        _i32(t, nm)
+    _contig(bcx, "bcx"); _contig(out, "out"); _contig(state, "state"); _contig(taps, "taps")
+    n_rows = cu_q.numel() - 1
+    lib = load_library("shortconv")
+    _check(lib.tuff_shortconv(_ptr(bcx), _ptr(out), dtype_code(out), _ptr(taps), _ptr(state), _ptr(slot_of_row),
+                              _ptr(row_of_token), _ptr(cu_q), c_int(n), c_int(n_rows), c_int(d), c_int(K),
+                              _stream()), "shortconv")
+
+
+# ------------------------------------------------------------------- attention
+def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None,
+                       inv_freq: torch.Tensor | None, positions: torch.Tensor, row_of_token: torch.Tensor,
+                       block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
+                       v_pages: torch.Tensor | None, H: int, G: int, hd: int, rot_dim: int, eps: float,
+                       write_kv: bool = True) -> None:
+    """Per-head RMSNorm + NeoX rotation of q and k in place; K and V stored in their pages.
+
+    k_pages / v_pages: [num_pages, G, page_size, hd]; block_table: [rows, max_blocks] int32.
+    """
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (H + 2 * G) * hd
+    _contig(qkv, "qkv"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
+    page_size, max_blocks = 1, 0
+    if write_kv:
+        assert k_pages is not None and v_pages is not None and block_table is not None
+        assert k_pages.shape == v_pages.shape and k_pages.shape[1] == G and k_pages.shape[3] == hd
+        assert k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype
+        _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
+        _i32(block_table, "block_table")
+        page_size, max_blocks = k_pages.shape[2], block_table.shape[1]
+    if rot_dim:
+        assert inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2
+    for wv in (q_norm_w, k_norm_w):
+        assert wv is None or (wv.dtype == torch.float32 and wv.numel() == hd)
+    lib = load_library("attention_plain")
+    _check(lib.tuff_qk_norm_rope_write(_ptr(qkv), dtype_code(qkv), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+                                       _ptr(positions), _ptr(row_of_token), _ptr(block_table), c_int(max_blocks),
+                                       _ptr(k_pages), _ptr(v_pages), c_int(n), c_int(H), c_int(G), c_int(hd),
+                                       c_int(rot_dim), c_int(page_size), c_float(eps), c_int(1 if write_kv else 0),
+                                       _stream()), "qk_norm_rope_write")
+
+
+def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                          positions: torch.Tensor, row_of_token: torch.Tensor, out: torch.Tensor, H: int, G: int,
+                          hd: int, scale: float, window: int = 0) -> None:
+    """Causal attention of each token over its request's cached keys (the last `window` if > 0).
+
+    q: [n, >= H*hd] (row stride taken from the tensor), out: [n, H*hd].
+    """
+    n = q.shape[0]
+    assert q.stride(1) == 1 and out.shape == (n, H * hd) and q.dtype == k_pages.dtype == out.dtype
+    _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
+    _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
+    lib = load_library("attention_plain")
+    _check(lib.tuff_paged_attention_plain(_ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+                                          dtype_code(q), _ptr(block_table), c_int(block_table.shape[1]),
+                                          _ptr(positions), _ptr(row_of_token), _ptr(out), c_int(n), c_int(H),
+                                          c_int(G), c_int(hd), c_int(k_pages.shape[2]), c_float(scale),
+                                          c_int(window), _stream()), "paged_attention_plain")
+
+
+def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
+                    window: int = 0, **_hints) -> None:
+    paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window)
+
+
+# -------------------------------------------------------------------- sampling
+SAMPLE_ROW_FORMAT = "<ffffiiQQQ"     # temp, top_p, min_p, repeat_penalty, top_k, n_recent, seed, request key, token index
+SAMPLE_ROW_BYTES = struct.calcsize(SAMPLE_ROW_FORMAT)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == n
+    _contig(logits, "logits")
+    lib = load_library("sampling")
+    _check(lib.tuff_argmax(_ptr(logits), c_int(n), c_int(V), _ptr(out), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, rows: torch.Tensor, recent: torch.Tensor | None, work: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """Samples one token per logits row; `rows` holds packed SAMPLE_ROW_FORMAT records (uint8 tensor)."""
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == n
+    assert rows.dtype == torch.uint8 and rows.numel() == n * SAMPLE_ROW_BYTES
+    assert work.dtype == torch.float32 and work.numel() >= n * V
+    _contig(logits, "logits"); _i32(recent, "recent")
+    lib = load_library("sampling")
+    assert lib.tuff_sample_row_bytes() == SAMPLE_ROW_BYTES
+    max_recent = 0 if recent is None else recent.shape[1]
+    _check(lib.tuff_sample(_ptr(logits), c_int(n), c_int(V), _ptr(rows), _ptr(recent), c_int(max_recent),
+                           _ptr(work), _ptr(out), _stream()), "sample")

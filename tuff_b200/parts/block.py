@@ -1,0 +1,15 @@
+"""Arrangements of a layer's parts.  `prenorm`: x += mixer(norm_a(x)), then
+x += ffn(norm_b(x)), the residual stream staying in fp32 throughout
+(reference: src/lfm25_engine.c:365-423)."""
+from __future__ import annotations
+
+from .base import Block, register_block
+
+
+@register_block("prenorm")
+class PreNormBlock(Block):
+    def forward(self, ctx, x, layer, cache, reads_only=False):
+        h = layer.mixer_norm.forward(ctx, x)
+        layer.mixer.forward(ctx, cache, h, x, reads_only)
+        h = layer.ffn_norm.forward(ctx, x)
+        layer.ffn.forward(ctx, h, x)

@@ -1,0 +1,24 @@
+"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, statistics in fp32; the weight
+multiplies directly, with no "+1" (reference: src/lfm25_gpu.cu:207-262, weight
+use at :244; eps from the model file, src/lfm25_model.c:92-93)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import Norm, WeightDecl, register_norm
+
+
+@register_norm("rmsnorm")
+class RMSNorm(Norm):
+    def __init__(self, dim: int, eps: float):
+        self.dim, self.eps = int(dim), float(eps)
+
+    def weight_decls(self):
+        return {"weight": WeightDecl((self.dim,), role="vector", init="norm")}
+
+    def forward(self, ctx, x, row_index=None):
+        n = x.shape[0] if row_index is None else row_index.numel()
+        out = torch.empty((n, self.dim), dtype=self.act_dtype, device=x.device)
+        ops.rmsnorm(x, self.w["weight"], self.eps, out, row_index)
+        return out
