@@ -1,0 +1,298 @@
+"""Each CUDA kernel alone against a plain fp32/fp64 reference of the same
+operation, at sizes other than the engine's tests use (head sizes in steps of
+16, widths and vocabularies that are no power of two, odd row counts)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a)).to(dtype).cuda()
+
+
+def close(got, ref, dtype, scale=1.0):
+    got = got.float().cpu().numpy().astype(np.float64)
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    err = np.abs(got - ref).max()
+    assert err <= tol * scale * max(1.0, np.abs(ref).max()), f"max error {err:.3g}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,V,n", [(80, 301, 7), (2048, 1000, 3), (17, 5, 33)])
+def test_embed(dtype, d, V, n):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(0)
+    table = dev(rng.normal(size=(V, d)), DT[dtype])
+    toks = rng.integers(0, V, n)
+    out = torch.empty(n, d, device="cuda")
+    ops.embed(dev(toks, torch.int32), table, out)
+    assert torch.equal(out, table.float()[torch.as_tensor(toks).cuda()])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,n,eps", [(80, 5, 1e-5), (2048, 3, 1e-6), (333, 9, 1e-3), (4096 + 16, 2, 1e-5)])
+def test_rmsnorm(dtype, d, n, eps):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(1)
+    x = rng.normal(size=(n, d)) * 3
+    w = 1 + 0.1 * rng.normal(size=d)
+    xd, wd = dev(x), dev(w)
+    out = torch.empty(n, d, dtype=DT[dtype], device="cuda")
+    ops.rmsnorm(xd, wd, eps, out)
+    close(out, plain.rms_norm(xd.cpu().numpy().astype(np.float64), wd.cpu().numpy().astype(np.float64), eps), dtype)
+    idx = dev([n - 1, 0, n - 1], torch.int32)
+    out2 = torch.empty(3, d, dtype=DT[dtype], device="cuda")
+    ops.rmsnorm(xd, wd, eps, out2, idx)
+    assert torch.equal(out2, out[[n - 1, 0, n - 1]])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K", [(1, 301, 80), (7, 130, 200), (65, 64, 48), (130, 257, 1000), (3, 2048, 5632)])
+def test_linear(dtype, M, N, K):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(2)
+    a = dev(rng.normal(size=(M, K)), DT[dtype])
+    w = dev(rng.normal(size=(N, K)) * 0.05, DT[dtype])
+    ref = a.double().cpu().numpy() @ w.double().cpu().numpy().T
+    out = torch.empty(M, N, dtype=DT[dtype], device="cuda")
+    ops.linear(a, w, out)
+    close(out, ref, dtype, scale=2.0)
+    res = dev(rng.normal(size=(M, N)))
+    acc = res.clone()
+    ops.linear(a, w, acc, accumulate=True)                 # the residual stream takes the product in fp32
+    close(acc, res.double().cpu().numpy() + ref, "float32" if dtype == "float32" else dtype, scale=2.0)
+    logits = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.linear(a, w, logits)
+    close(logits, ref, "float32", scale=4.0 if dtype == "float32" else 1.0)   # fp32 out even from bf16 operands
+
+
+def test_linear_is_batch_invariant():
+    """A row's fp32 result does not depend on how many rows run with it."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(3)
+    a = dev(rng.normal(size=(70, 333)))
+    w = dev(rng.normal(size=(129, 333)))
+    full = torch.empty(70, 129, device="cuda")
+    ops.linear(a, w, full)
+    for lo, hi in ((0, 1), (5, 7), (63, 70)):
+        part = torch.empty(hi - lo, 129, device="cuda")
+        ops.linear(a[lo:hi].contiguous(), w, part)
+        assert torch.equal(part, full[lo:hi])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("F,n", [(200, 5), (5632, 3), (33, 17)])
+def test_swiglu(dtype, F, n):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(4)
+    gu = dev(rng.normal(size=(n, 2 * F)) * 2, DT[dtype])
+    out = torch.empty(n, F, dtype=DT[dtype], device="cuda")
+    ops.swiglu(gu, out)
+    g, u = gu.double().cpu().numpy()[:, :F], gu.double().cpu().numpy()[:, F:]
+    close(out, g / (1 + np.exp(-g)) * u, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,K,lens", [(80, 3, (5, 1, 2, 9)), (96, 4, (1, 1, 1)), (200, 2, (7, 2)), (64, 5, (3, 2, 1, 11))])
+def test_shortconv_continues_state(dtype, d, K, lens):
+    """Portions of any length (also shorter than K-1) continue each row's state; slots are not
+    in row order; the rolled state equals the last K-1 values of u."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(5)
+    R, T = len(lens), sum(lens)
+    taps = rng.normal(size=(d, K))
+    n_slots = R + 2
+    slots = rng.permutation(n_slots)[:R]
+    state0 = rng.normal(size=(n_slots, K - 1, d))
+    bcx = dev(rng.normal(size=(T, 3 * d)), DT[dtype])
+    b64 = bcx.double().cpu().numpy()
+    state = dev(state0)
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    out = torch.empty(T, d, dtype=DT[dtype], device="cuda")
+    ops.shortconv(bcx, dev(taps), state, dev(slots, torch.int32),
+                  dev(np.repeat(np.arange(R), lens), torch.int32), dev(cu, torch.int32), out)
+    taps32 = dev(taps).double().cpu().numpy()
+    st32 = dev(state0).double().cpu().numpy()
+    new_state = state.double().cpu().numpy()
+    for r in range(R):
+        seg = b64[cu[r]:cu[r + 1]]
+        u = np.concatenate([st32[slots[r]], seg[:, :d] * seg[:, 2 * d:]], 0)
+        y = sum(taps32[:, j][None] * u[j:j + lens[r]] for j in range(K))
+        close(out[cu[r]:cu[r + 1]], seg[:, d:2 * d] * y, dtype)
+        np.testing.assert_allclose(new_state[slots[r]], u[-(K - 1):], rtol=1e-6, atol=1e-6)
+    untouched = [s for s in range(n_slots) if s not in slots]
+    np.testing.assert_array_equal(new_state[untouched], st32[untouched])
+
+
+def paged_setup(rng, seqs, G, hd, page, dtype, n_pages=None):
+    """Scatters each sequence's keys/values over shuffled pages; returns pages and block tables."""
+    blocks = [math.ceil(s / page) for s in seqs]
+    n_pages = n_pages or sum(blocks) + 3
+    perm = rng.permutation(n_pages)
+    kp = torch.zeros(n_pages, G, page, hd, dtype=DT[dtype], device="cuda")
+    vp = torch.zeros_like(kp)
+    kp.fill_(float("nan")); vp.fill_(float("nan"))          # a read outside a request's keys would show
+    table = np.full((len(seqs), max(blocks)), -1, np.int32)
+    o = 0
+    for r, b in enumerate(blocks):
+        table[r, :b] = perm[o:o + b]
+        o += b
+    return kp, vp, table
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,hd,page,rot", [(4, 2, 16, 4, 16), (6, 3, 48, 8, 48), (8, 1, 80, 16, 32), (2, 2, 128, 2, 0),
+                                             (5, 5, 256, 64, 256)])
+def test_qk_norm_rope_write_and_attention(dtype, H, G, hd, page, rot):
+    """The fused q/k kernel and the paged attention together against the plain attention, for
+    rows that continue at different positions; pages are scattered and other pages hold NaN."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(6)
+    theta, eps = 12345.0, 1e-5
+    starts, lens = (0, 37, 5), (9, 1, 12)
+    seqs = [s + n for s, n in zip(starts, lens)]
+    kp, vp, table = paged_setup(rng, seqs, G, hd, page, dtype)
+    qn, kn = 1 + 0.1 * rng.normal(size=hd), 1 + 0.1 * rng.normal(size=hd)
+    inv_freq = (theta ** (-2.0 * np.arange(rot // 2) / rot)).astype(np.float32) if rot else None
+    full = [rng.normal(size=(s, (H + 2 * G) * hd)) for s in seqs]
+    tb = dev(table, torch.int32)
+
+    def run(rows_tokens):      # rows_tokens: list of (row, first position, count)
+        pos = np.concatenate([np.arange(p0, p0 + n) for _, p0, n in rows_tokens])
+        rot_ = np.concatenate([np.full(n, r) for r, _, n in rows_tokens])
+        qkv = dev(np.concatenate([full[r][p0:p0 + n] for r, p0, n in rows_tokens]), DT[dtype])
+        ops.qk_norm_rope_write(qkv, dev(qn), dev(kn), None if inv_freq is None else dev(inv_freq),
+                               dev(pos, torch.int32), dev(rot_, torch.int32), tb, kp, vp, H, G, hd, rot, eps)
+        out = torch.empty(len(pos), H * hd, dtype=DT[dtype], device="cuda")
+        ops.paged_attention(qkv, kp, vp, tb, dev(pos, torch.int32), dev(rot_, torch.int32), out, H, G, hd,
+                            1 / math.sqrt(hd))
+        return out
+
+    # first the earlier parts of rows 1 and 2 (their "cache"), then the step under test
+    run([(1, 0, starts[1]), (2, 0, starts[2])])
+    out = run([(r, starts[r], lens[r]) for r in range(3)])
+    o = 0
+    for r in range(3):
+        x = dev(full[r], DT[dtype]).double().cpu().numpy().reshape(seqs[r], H + 2 * G, hd)
+        q, k, v = x[:, :H], x[:, H:H + G], x[:, H + G:]
+        q, k = plain.rms_norm(q, qn.astype(np.float32), eps), plain.rms_norm(k, kn.astype(np.float32), eps)
+        if rot:
+            q = plain.rope_neox(q, np.arange(seqs[r]), theta, rot)
+            k = plain.rope_neox(k, np.arange(seqs[r]), theta, rot)
+        ref = np.zeros((seqs[r], H, hd))
+        for h in range(H):
+            g = h // (H // G)
+            s = q[:, h] @ k[:, g].T / math.sqrt(hd)
+            s = np.where(np.triu(np.ones((seqs[r], seqs[r]), bool), 1), -np.inf, s)
+            p = np.exp(s - s.max(-1, keepdims=True))
+            ref[:, h] = (p / p.sum(-1, keepdims=True)) @ v[:, g]
+        close(out[o:o + lens[r]], ref[starts[r]:].reshape(lens[r], H * hd), dtype, scale=3.0)
+        o += lens[r]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_a_far_key_and_respects_the_window(dtype):
+    """One key among hundreds matches the query (score far above the rest): the output must be
+    that key's value, wherever its page lies; with a window that ends just after it, it must not."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(7)
+    H = G = 1
+    hd, page, n = 32, 8, 700
+    kp, vp, table = paged_setup(rng, [n], G, hd, page, dtype)
+    keys = rng.normal(size=(n, hd)) * 0.1
+    vals = rng.normal(size=(n, hd))
+    q = rng.normal(size=hd)
+    for far in (0, 7, 8, 333, 698):
+        k2 = keys.copy()
+        k2[far] = q * 4.0                       # q.k = 4 |q|^2 ~ 128, every other score ~ 0.5
+        for p in range(n):
+            pg, off = table[0, p // page], p % page
+            kp[pg, 0, off] = dev(k2[p], DT[dtype]); vp[pg, 0, off] = dev(vals[p], DT[dtype])
+        qd = dev(q[None], DT[dtype])
+        out = torch.empty(1, hd, dtype=DT[dtype], device="cuda")
+        args = (qd, kp, vp, dev(table, torch.int32), dev([n - 1], torch.int32), dev([0], torch.int32), out, 1, 1, hd, 1.0)
+        ops.paged_attention(*args)
+        close(out, dev(vals[far], DT[dtype]).double().cpu().numpy()[None], dtype)
+        w_in, w_out = n - far, n - far - 1       # the window that just holds the key / just misses it
+        ops.paged_attention(*args, window=w_in)
+        close(out, dev(vals[far], DT[dtype]).double().cpu().numpy()[None], dtype)
+        if w_out >= 1:
+            ops.paged_attention(*args, window=w_out)
+            assert (out.float().cpu().numpy() - vals[far]).std() > 0.3
+
+
+@pytest.mark.parametrize("V", [301, 65536, 5, 1025])
+def test_argmax_first_maximum(V):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(8)
+    l = rng.normal(size=(6, V)).astype(np.float32)
+    l[1, [V // 2, V - 1]] = 9.0                     # a tie: the lower index wins
+    l[2, :] = -1.0                                  # all equal: index 0
+    l[3, V - 1] = 50.0
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    ops.argmax(dev(l), out)
+    ref = [int(r.argmax()) for r in l]
+    assert out.tolist() == ref and ref[1] == V // 2 and ref[2] == 0 and ref[3] == V - 1
+
+
+@pytest.mark.parametrize("V", [301, 4096, 65536])
+def test_sampling_chain_matches_plain(V):
+    from tuff_b200.sampling import Sampler, SamplingParams, SampleRow
+    rng = np.random.default_rng(9)
+    cases = [
+        SamplingParams(temp=0.8, seed=2),
+        SamplingParams(temp=1.5, top_k=5, seed=3),
+        SamplingParams(temp=0.7, top_p=0.6, seed=4),
+        SamplingParams(temp=1.0, min_p=0.2, seed=5),
+        SamplingParams(temp=0.9, top_k=40, top_p=0.9, min_p=0.02, repeat_penalty=1.3, repeat_last_n=8, seed=6),
+        SamplingParams(temp=0.0),
+        SamplingParams(temp=2.0, top_k=1, seed=7),
+        SamplingParams(temp=1.0, top_p=0.3, seed=8),
+    ]
+    logits = (rng.normal(size=(len(cases), V)) * 3).astype(np.float32)
+    logits[1, :10] = 7.0                           # ties across the top-k edge
+    logits[7, [3, 9]] = 12.0                       # two equal leaders at the nucleus edge
+    recent = [list(rng.integers(0, V, 12)) for _ in cases]
+    sampler = Sampler(V, "cuda:0")
+    ld = dev(logits)
+    hits = 0
+    for tok_index in range(24):
+        rows = [SampleRow(p, 100 + i, tok_index, recent[i]) for i, p in enumerate(cases)]
+        got = sampler.sample(ld, rows).tolist()
+        for i, p in enumerate(cases):
+            u = plain.uniform_draw(p.seed, 100 + i, tok_index)
+            rec = recent[i][-p.repeat_last_n:] if p.repeat_penalty > 1 else ()
+            want = plain.sample_token(logits[i], p.temp, p.top_k, p.top_p, p.min_p, p.repeat_penalty, rec, u)
+            hits += got[i] == want
+            if got[i] != want:       # only a draw that lands on a boundary within fp32 rounding may differ
+                w64 = np.exp((logits[i].astype(np.float64) - logits[i].max()) / p.temp)
+                cum = np.cumsum(w64 / w64.sum())
+                assert p.temp > 0 and min(abs(cum - u)) < 1e-4, (i, tok_index, got[i], want)
+    assert hits >= 24 * len(cases) - 2
+    # the draw of a row does not depend on the rows beside it
+    solo = sampler.sample(ld[4:5], [SampleRow(cases[4], 104, 5, recent[4])]).tolist()
+    both = sampler.sample(ld, [SampleRow(p, 100 + i, 5, recent[i]) for i, p in enumerate(cases)]).tolist()
+    assert solo[0] == both[4]
+
+
+def test_temperature_sampling_follows_the_distribution():
+    from tuff_b200.sampling import Sampler, SamplingParams, SampleRow
+    V = 50
+    rng = np.random.default_rng(10)
+    l = rng.normal(size=V).astype(np.float32) * 2
+    p = np.exp(l.astype(np.float64) / 0.7); p /= p.sum()
+    sampler = Sampler(V, "cuda:0")
+    n = 4000
+    ld = dev(np.tile(l, (n, 1)))
+    sp = SamplingParams(temp=0.7, seed=11)
+    toks = np.array(sampler.sample(ld, [SampleRow(sp, 1, i) for i in range(n)]).tolist())
+    freq = np.bincount(toks, minlength=V) / n
+    assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() / n) + 0.01

@@ -1,0 +1,346 @@
+"""The parts alone (each against the plain implementation's function), schedules
+that name a layer twice or let a layer read another layer's cache, and a toy
+mixer with state of its own that is registered, built and stepped from this
+file alone."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+from tuff_b200.cache import CacheManager
+from tuff_b200.engine.batch import StepEntry, layout_entries, to_device
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 3e-5, "bfloat16": 3e-2}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a)).to(dtype).cuda()
+
+
+def f64(t):
+    return t.double().cpu().numpy()
+
+
+def close(got, ref, dtype, scale=1.0):
+    err = np.abs(f64(got) - ref).max()
+    assert err <= TOL[dtype] * scale * max(1.0, np.abs(ref).max()), f"max error {err:.3g}"
+
+
+def bind_random(part, dtype, rng, std=0.05):
+    w = {}
+    for n, d in part.weight_decls().items():
+        a = 1 + 0.1 * rng.normal(size=d.shape) if d.init == "norm" else std * rng.normal(size=d.shape)
+        w[n] = dev(a, torch.float32 if d.role == "vector" else DT[dtype])
+    part.bind(dict(w), DT[dtype])
+    return {n: f64(t) for n, t in w.items()}
+
+
+def make_ctx(cm, dtype, portions, vocab=100):
+    """portions: list of (request cache, n tokens); reserves pages and lays the step out."""
+    entries = [StepEntry(rc, [1] * n, []) for rc, n in portions]
+    for e in entries:
+        cm.reserve(e.cache, len(e.tokens))
+    return to_device(layout_entries(entries, cm), torch.device("cuda:0"), DT[dtype]), entries
+
+
+def run_part_in_portions(part, cm, storage, dtype, hs, cuts):
+    """Feeds each sequence of `hs` through `part` (a mixer) cut at `cuts`, several requests per step."""
+    rcs = [cm.open(i) for i in range(len(hs))]
+    outs = [[] for _ in hs]
+    pos = [0] * len(hs)
+    while any(p < len(h) for p, h in zip(pos, hs)):
+        step = []
+        for i, h in enumerate(hs):
+            if pos[i] < len(h):
+                n = min(cuts[(pos[i] + i) % len(cuts)], len(h) - pos[i])
+                step.append((i, n))
+        ctx, entries = make_ctx(cm, dtype, [(rcs[i], n) for i, n in step])
+        x = torch.cat([dev(hs[i][pos[i]:pos[i] + n], DT[dtype]) for i, n in step])
+        res = torch.zeros(x.shape[0], x.shape[1], device="cuda")
+        part.forward(ctx, storage, x, res)
+        o = 0
+        for (i, n), e in zip(step, entries):
+            outs[i].append(f64(res[o:o + n]))
+            cm.commit(e.cache, n)
+            pos[i] += n
+            o += n
+    for rc in rcs:
+        cm.close(rc)
+    return [np.concatenate(o) for o in outs]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,K", [(80, 3), (48, 4), (112, 2)])
+def test_gated_short_conv_part(dtype, d, K):
+    from tuff_b200.parts import MIXERS, PartSpec
+    rng = np.random.default_rng(0)
+    part = MIXERS.build(PartSpec("gated_short_conv", dict(d_model=d, kernel_size=K)))
+    w = bind_random(part, dtype, rng, std=0.2)
+    cm = CacheManager([part.cache_need()], page_size=4, max_tokens=64, max_requests=3, dtype=DT[dtype], device="cuda:0")
+    hs = [f64(dev(rng.normal(size=(n, d)), DT[dtype])) for n in (23, 9, 14)]
+    got = run_part_in_portions(part, cm, cm.storages[0], dtype, hs, cuts=(1, 5, 2, 3, 1, 1, 8))
+    for g, h in zip(got, hs):
+        ref = plain.short_conv_mixer(h, w["in_proj"], w["conv"].reshape(d, K), w["out_proj"])
+        err = np.abs(g - ref).max()
+        assert err <= TOL[dtype] * 2 * max(1, np.abs(ref).max()), err
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,H,G,hd,page,window", [(64, 4, 2, 16, 4, None), (80, 6, 3, 48, 8, None), (96, 4, 1, 32, 2, 7),
+                                                  (72, 2, 2, 64, 16, None)])
+def test_gqa_attention_part(dtype, d, H, G, hd, page, window):
+    from tuff_b200.parts import MIXERS, PartSpec
+    rng = np.random.default_rng(1)
+    theta, eps = 5e4, 1e-6
+    part = MIXERS.build(PartSpec("gqa_attention", dict(
+        d_model=d, num_heads=H, num_kv_heads=G, head_dim=hd, qk_norm_eps=eps, window=window,
+        position_encoding=PartSpec("rope_neox", dict(head_dim=hd, theta=theta)))))
+    w = bind_random(part, dtype, rng, std=0.3)
+    cm = CacheManager([part.cache_need()], page_size=page, max_tokens=128, max_requests=3, dtype=DT[dtype],
+                      device="cuda:0")
+    hs = [f64(dev(rng.normal(size=(n, d)), DT[dtype])) for n in (41, 6, 30)]
+    got = run_part_in_portions(part, cm, cm.storages[0], dtype, hs, cuts=(3, 1, 7, 2, 1, 12))
+    for g, h in zip(got, hs):
+        ref = plain.gqa_attention_mixer(h, w["q_proj"], w["k_proj"], w["v_proj"], w["out_proj"], w["q_layernorm"],
+                                        w["k_layernorm"], H, G, hd, eps, theta, window=window)
+        err = np.abs(g - ref).max()
+        assert err <= TOL[dtype] * 4 * max(1, np.abs(ref).max()), err
+    cm.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu_norm_embedding_head_parts(dtype):
+    from tuff_b200.parts import EMBEDDINGS, FEED_FORWARDS, HEADS, NORMS, PartSpec
+    rng = np.random.default_rng(2)
+    d, F, V, T = 80, 200, 301, 11
+    ffn = FEED_FORWARDS.build(PartSpec("swiglu", dict(d_model=d, ffn_dim=F)))
+    wf = bind_random(ffn, dtype, rng, std=0.2)
+    norm = NORMS.build(PartSpec("rmsnorm", dict(dim=d, eps=1e-5)))
+    wn = bind_random(norm, dtype, rng)
+    emb = EMBEDDINGS.build(PartSpec("token_embedding", dict(vocab_size=V, d_model=d)))
+    we = bind_random(emb, dtype, rng, std=1.0)
+    head = HEADS.build(PartSpec("lm_head", dict(vocab_size=V, d_model=d)))
+    wh = bind_random(head, dtype, rng, std=0.2)
+    cm = CacheManager([], page_size=4, max_tokens=64, max_requests=2, device="cuda:0")
+    rc = cm.open("a")
+    toks = rng.integers(0, V, T).tolist()
+    e = StepEntry(rc, toks, [0, 4, T - 1])
+    cm.reserve(rc, T)
+    ctx = to_device(layout_entries([e], cm), torch.device("cuda:0"), DT[dtype])
+    x = emb.forward(ctx)
+    np.testing.assert_array_equal(f64(x), we["weight"][toks])
+    h = norm.forward(ctx, x)
+    close(h, plain.rms_norm(f64(x), wn["weight"], 1e-5), dtype)
+    res = x.clone()
+    ffn.forward(ctx, h, res)
+    close(res, f64(x) + plain.swiglu_ffn(f64(h), wf["w1"], wf["w3"], wf["w2"]), dtype, scale=2)
+    logits = head.forward(ctx, res, norm)
+    assert logits.dtype == torch.float32 and logits.shape == (3, V)
+    close(logits, plain.lm_head(f64(res)[[0, 4, T - 1]], wn["weight"], 1e-5, wh["weight"]), dtype, scale=2)
+
+
+# ------------------------------------------------------------------ toy parts
+def register_toy_parts():
+    """A mixer with state of its own (an exponential moving average per channel, with a
+    learned decay), defined here and nowhere in the package."""
+    from tuff_b200.parts import Mixer, StateNeed, WeightDecl, register_mixer, MIXERS
+    if "toy_ema" in MIXERS.kinds():
+        return
+
+    @register_mixer("toy_ema")
+    class ToyEma(Mixer):
+        def __init__(self, d_model):
+            self.d = d_model
+
+        def weight_decls(self):
+            return {"decay": WeightDecl((self.d,), role="vector", init="norm"),
+                    "proj": WeightDecl((self.d, self.d))}
+
+        def cache_need(self):
+            return StateNeed(shape=(self.d,), dtype="float32")
+
+        def forward(self, ctx, cache, h, residual, reads_only=False):
+            a = torch.sigmoid(self.w["decay"])
+            cu, slots = ctx.host["cu_q"], ctx.host["slot_of_row"]
+            y = torch.empty_like(h, dtype=torch.float32)
+            for r in range(ctx.n_rows):
+                s = cache.state[int(slots[r])]
+                for t in range(int(cu[r]), int(cu[r + 1])):
+                    s = a * s + (1 - a) * h[t].float()
+                    y[t] = s
+                cache.state[int(slots[r])] = s
+            residual += (y.to(h.dtype) @ self.w["proj"].T).float()
+
+
+def toy_architecture():
+    """A whole toy architecture around the toy mixer, registered from the test."""
+    from tuff_b200.config import Architecture, register_architecture
+    from tuff_b200.models import LayerSpec, ModelSpec
+    from tuff_b200.parts import PartSpec
+    register_toy_parts()
+
+    def spec(cfg):
+        d, V = cfg["d"], cfg["vocab"]
+        layers = []
+        for i, kind in enumerate(cfg["kinds"]):
+            p = f"l{i}."
+            if kind == "ema":
+                mixer = PartSpec("toy_ema", dict(d_model=d), {"decay": p + "decay", "proj": p + "proj"})
+            else:
+                mixer = PartSpec("gqa_attention", dict(d_model=d, num_heads=2, num_kv_heads=1, head_dim=16,
+                                                       qk_norm_eps=None, position_encoding=None),
+                                 {n: p + n for n in ("q_proj", "k_proj", "v_proj", "out_proj")})
+            layers.append(LayerSpec(
+                mixer=mixer, ffn=PartSpec("swiglu", dict(d_model=d, ffn_dim=cfg["ffn"]),
+                                          {n: p + n for n in ("w1", "w2", "w3")}),
+                mixer_norm=PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": p + "n1"}),
+                ffn_norm=PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": p + "n2"})))
+        return ModelSpec("ToyEmaLM", d, V, PartSpec("token_embedding", dict(vocab_size=V, d_model=d), {"weight": "emb"}),
+                         layers, PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": "nf"}),
+                         PartSpec("lm_head", dict(vocab_size=V, d_model=d), {"weight": "emb"}))
+
+    register_architecture(Architecture("ToyEmaLM", lambda raw, where: raw, spec, lambda c: dict(c)))
+
+
+def toy_plain_forward(folder, tokens):
+    cfg = plain.read_config(folder)
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    x = w["emb"][tokens]
+    d = cfg["d"]
+    for i, kind in enumerate(cfg["kinds"]):
+        p = f"l{i}."
+        h = plain.rms_norm(x, w[p + "n1"], 1e-5)
+        if kind == "ema":
+            a = 1 / (1 + np.exp(-w[p + "decay"]))
+            s, y = np.zeros(d), np.zeros_like(h)
+            for t in range(len(tokens)):
+                s = a * s + (1 - a) * h[t]
+                y[t] = s
+            o = y @ w[p + "proj"].T
+        else:
+            o = plain.gqa_attention_mixer(h, w[p + "q_proj"], w[p + "k_proj"], w[p + "v_proj"], w[p + "out_proj"],
+                                          None, None, 2, 1, 16, 0.0, None)
+        x = x + o
+        x = x + plain.swiglu_ffn(plain.rms_norm(x, w[p + "n2"], 1e-5), w[p + "w1"], w[p + "w3"], w[p + "w2"])
+    return plain.lm_head(x, w["nf"], 1e-5, w["emb"])
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    from tuff_b200.engine import ModelRunner
+    from tuff_b200.weights import write_random_model
+    toy_architecture()
+    cfg = dict(architectures=["ToyEmaLM"], d=48, vocab=97, ffn=64, kinds=["ema", "attention", "ema"])
+    folder = write_random_model(str(tmp_path / "toy"), cfg, 5, store_dtype=torch.float32)
+    runner = ModelRunner(folder, dtype="float32", max_tokens=64, page_size=4, max_requests=2)
+    assert [type(s).__name__ for s in runner.cache.storages] == ["StateStorage", "PagedStorage", "StateStorage"]
+    rng = np.random.default_rng(3)
+    seqs = {"a": rng.integers(0, 97, 19).tolist(), "b": rng.integers(0, 97, 11).tolist()}
+    refs = {k: toy_plain_forward(folder, v) for k, v in seqs.items()}
+    rcs = {k: runner.open(k) for k in seqs}
+    pos = {k: 0 for k in seqs}
+    cuts = {"a": [4, 1, 1, 6, 2, 5], "b": [2, 3, 1, 1, 4]}
+    while any(pos[k] < len(seqs[k]) for k in seqs):
+        entries, keys = [], []
+        for k in seqs:
+            if pos[k] < len(seqs[k]):
+                n = cuts[k].pop(0)
+                entries.append(StepEntry(rcs[k], seqs[k][pos[k]:pos[k] + n], list(range(n))))
+                keys.append((k, n))
+        logits = f64(runner.step(entries))
+        o = 0
+        for k, n in keys:
+            np.testing.assert_allclose(logits[o:o + n], refs[k][pos[k]:pos[k] + n], atol=2e-4, rtol=2e-4)
+            pos[k] += n
+            o += n
+    # a slot that is used again starts from zero state
+    runner.close(rcs["a"])
+    rc = runner.open("again")
+    logits = f64(runner.step([StepEntry(rc, seqs["a"], [len(seqs["a"]) - 1])]))
+    np.testing.assert_allclose(logits[0], refs["a"][-1], atol=2e-4, rtol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_names_a_layer_twice_and_shares_a_cache(tmp_path, dtype):
+    """The order of layers is data: layer 1 runs twice (with storage of its own each time) and
+    the last run of an attention layer reads the keys and values that an earlier one wrote."""
+    from tuff_b200.config import Architecture, register_architecture
+    from tuff_b200.engine import ModelRunner
+    from tuff_b200.models import ScheduleEntry
+    from tuff_b200.models.lfm2 import lfm2_spec
+    from tuff_b200.config import Lfm2Config
+    from tuff_b200.weights import write_random_model
+    from tiny import TINY_A
+
+    def spec(cfg):
+        s = lfm2_spec(cfg)
+        s.architecture = "Lfm2Looped"
+        # layers: 0 conv, 1 attention, 2 conv, 3 attention
+        s.schedule = [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(2, 2), ScheduleEntry(1, 3),
+                      ScheduleEntry(3, 1, reads_only=True)]
+        return s
+    register_architecture(Architecture("Lfm2Looped", Lfm2Config.from_dict, spec, lambda c: c.to_dict()))
+    raw = dict(TINY_A, architectures=["Lfm2Looped"])
+    folder = write_random_model(str(tmp_path / "looped"), raw, 3)
+    m = plain.PlainLfm2(folder)
+    w, d, eps = m.w, m.d, m.eps
+
+    def plain_forward(tokens):
+        x = plain.embed(w["model.embed_tokens.weight"], tokens)
+        kv_from = {}
+
+        def attn(i, h, shared_h=None):
+            a = f"model.layers.{i}.self_attn."
+            src = f"model.layers.{1 if shared_h is not None else i}.self_attn."
+            hk = h if shared_h is None else shared_h
+            T = len(tokens)
+            pos = np.arange(T)
+            q = plain.rope_neox(plain.rms_norm((h @ w[a + "q_proj.weight"].T).reshape(T, m.H, m.hd),
+                                               w[a + "q_layernorm.weight"], eps), pos, m.theta)
+            k = plain.rope_neox(plain.rms_norm((hk @ w[src + "k_proj.weight"].T).reshape(T, m.G, m.hd),
+                                               w[src + "k_layernorm.weight"], eps), pos, m.theta)
+            v = (hk @ w[src + "v_proj.weight"].T).reshape(T, m.G, m.hd)
+            out = np.zeros((T, m.H, m.hd))
+            for hh in range(m.H):
+                g = hh // (m.H // m.G)
+                s = q[:, hh] @ k[:, g].T / math.sqrt(m.hd)
+                s = np.where(np.triu(np.ones((T, T), bool), 1), -np.inf, s)
+                p = np.exp(s - s.max(-1, keepdims=True))
+                out[:, hh] = (p / p.sum(-1, keepdims=True)) @ v[:, g]
+            return out.reshape(T, -1) @ w[a + "out_proj.weight"].T
+
+        first_h1 = None
+        for layer, shared in ((0, False), (1, False), (2, False), (1, False), (3, True)):
+            p = f"model.layers.{layer}."
+            h = plain.rms_norm(x, w[p + "operator_norm.weight"], eps)
+            if layer in (0, 2):
+                o = plain.short_conv_mixer(h, w[p + "conv.in_proj.weight"], w[p + "conv.conv.weight"].reshape(d, 3),
+                                           w[p + "conv.out_proj.weight"])
+            elif shared:
+                o = attn(3, h, shared_h=first_h1)
+            else:
+                if first_h1 is None:
+                    first_h1 = h
+                o = attn(1, h)
+            x = x + o
+            f = p + "feed_forward."
+            x = x + plain.swiglu_ffn(plain.rms_norm(x, w[p + "ffn_norm.weight"], eps), w[f + "w1.weight"],
+                                     w[f + "w3.weight"], w[f + "w2.weight"])
+        return plain.lm_head(x, w["model.embedding_norm.weight"], eps, w["model.embed_tokens.weight"])
+
+    runner = ModelRunner(folder, dtype=dtype, max_tokens=64, page_size=4, max_requests=2)
+    assert len(runner.cache.storages) == 4
+    toks = np.random.default_rng(4).integers(0, 256, 29).tolist()
+    ref = plain_forward(toks)
+    rc = runner.open("x")
+    got = []
+    for lo, hi in ((0, 9), (9, 10), (10, 12), (12, 29)):
+        got.append(f64(runner.step([StepEntry(rc, toks[lo:hi], list(range(hi - lo)))])))
+    got = np.concatenate(got)
+    tol = 2e-4 if dtype == "float32" else 5e-2
+    assert np.abs(got - ref).max() < tol, np.abs(got - ref).max()

@@ -46,6 +46,7 @@ class StepContext:
     max_q_len: int = 1                 # longest row of the step
     max_seq_len: int = 1               # longest request after the step
     all_single: bool = False           # every row brings exactly one token
+    host: Dict[str, object] = field(default_factory=dict)    # the same tables as NumPy arrays on the host
     extra: Dict[str, object] = field(default_factory=dict)   # room for parts defined elsewhere
 
 
@@ -127,4 +128,4 @@ def to_device(host: dict, device: torch.device, act_dtype: torch.dtype) -> StepC
                        n_wanted=host["want_index"].size, tokens=cut[0], positions=cut[1], row_of_token=cut[2],
                        cu_q=cut[3], slot_of_row=cut[4], want_index=cut[5], block_tables=tables,
                        max_q_len=host["max_q_len"], max_seq_len=host["max_seq_len"],
-                       all_single=host["all_single"])
+                       all_single=host["all_single"], host=host)
