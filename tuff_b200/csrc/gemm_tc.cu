@@ -1,0 +1,399 @@
+// bf16 matrix product on the Blackwell tensor cores:  C[M,N] (=|+=) A[M,K] * W[N,K]^T.
+//
+// Both operands are K-major ([rows, K] with K contiguous), which is how the
+// activations and the checkpoints' [out, in] matrices lie in memory.  One CTA
+// computes a 128 x BN tile: a producer thread streams 128x64 and BNx64 bf16
+// tiles into a ring of shared-memory stages with TMA (cp.async.bulk.tensor, 128-byte
+// swizzle), one thread issues tcgen05.mma (M=128, N=BN, K=16, fp32 accumulation in
+// tensor memory), and four warps read the accumulator back with tcgen05.ld and
+// write the result.  No cluster multicast is used anywhere.
+//
+// Which operand is the 128-row side is the launcher's choice:
+//   many tokens (prefill)   rows of A (tokens) x BN rows of W
+//   few tokens (decode)     rows of W (outputs) x BN >= tokens ("swapped"): the
+//                           weights stream through the 128-row side once, and the
+//                           K range is split over blockIdx.z so that all SMs pull on
+//                           HBM.  Partial sums go to a workspace and are added in a
+//                           fixed order by a second kernel, so the result does not
+//                           depend on timing.
+// The reference computes these products with per-row matrix-vector kernels on
+// quantised weights (src/lfm25_gpu.cu:148-202, 860-934); accumulation into the
+// residual is its accum=true (src/lfm25_engine.c:380,405,419).
+//
+// Every wait on an mbarrier is bounded: if it runs out, the kernel records a code
+// in *status, lets its copies in flight land, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;            // rows of the 128-row operand per CTA (UMMA M)
+constexpr int BK = 64;             // K elements per stage: 128 bytes of bf16, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
+constexpr uint32_t MAX_POLLS = 1u << 26;
+
+enum : int { OUT_STORE = 0, OUT_ACCUM = 1, OUT_PARTIAL = 2 };
+
+struct GemmParams {
+    void* out;            // [rows_of_tokens, ld] bf16 or fp32
+    float* partial;       // [splits, rows_of_tokens, n_out] fp32 (OUT_PARTIAL)
+    int* status;
+    long long ld;         // row stride of out, in elements
+    int a_rows, b_rows;   // rows of the 128-row operand and of the BN-row operand
+    int k_blocks;         // ceil(K / 64)
+    int kb_per_split;
+    int mode;             // OUT_*
+    int out_dtype;        // TUFF_F32 / TUFF_BF16
+    int swapped;          // 1: the 128-row operand is W, so D is [out, token]
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; on failure records `code` (first failure wins) and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    for (uint32_t i = 0; i < MAX_POLLS; ++i)
+        if (mbar_try(bar, parity)) return true;
+    atomicCAS(status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile [rows][64 bf16] written by TMA with 128-byte
+// swizzle: rows 128 bytes apart, groups of 8 rows 1024 bytes apart (the stride offset), version 1,
+// layout type 2 (SWIZZLE_128B).  The tile's base is 1024-byte aligned; a K step of 16 elements
+// moves the start address by 32 bytes inside the swizzled row.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major) = 16 B
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: fp32 accumulator, bf16 x bf16, both K-major, M=128, N=BN.
+template <int BN> __device__ __forceinline__ constexpr uint32_t instr_desc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN> constexpr int tmem_cols() { return BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256; }
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
+    static constexpr int BARS = TILES;                       // full[STAGES], empty[STAGES], accum_full
+    static constexpr int TMEM_SLOT = BARS + (2 * STAGES + 1) * 8;
+    static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;      // + room to align the base to 1024 bytes
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t a_tiles = base, b_tiles = base + STAGES * L::A_BYTES;
+    const uint32_t bars = base + L::BARS;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::TMEM_SLOT);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int kb0 = blockIdx.z * p.kb_per_split;
+    const int nkb = min(p.kb_per_split, p.k_blocks - kb0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(base + (uint32_t)L::TMEM_SLOT), "r"((uint32_t)tmem_cols<BN>()) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1);
+                if (!ok) break;
+                mbar_expect_tx(full_bar(s), L::A_BYTES + L::B_BYTES);
+                const int k = (kb0 + i) * BK;
+                tma_load_2d(a_tiles + s * L::A_BYTES, &map_a, full_bar(s), k, m0);
+                tma_load_2d(b_tiles + s * L::B_BYTES, &map_b, full_bar(s), k, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc<BN>();
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+                ok = mbar_wait(full_bar(s), ph, p.status, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a = a_tiles + s * L::A_BYTES, b = b_tiles + s * L::B_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                    umma(tmem_base, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
+                         (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(accum_bar);         // the accumulator is complete once all MMAs retire
+        }
+    } else {
+        ok = mbar_wait(accum_bar, 0, p.status, 3);
+        tc_fence_after();
+        if (ok) {
+            const int quad = warp & 3;                      // the 32 tensor-memory lanes this warp may read
+            const int row = m0 + quad * 32 + lane;          // row of the 128-row operand
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            float* partial = p.partial;
+            const int n_out = p.swapped ? p.a_rows : p.b_rows;
+            const int n_tok = p.swapped ? p.b_rows : p.a_rows;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (n0 + c0 >= p.b_rows) break;             // uniform over the warp
+                uint32_t r[16];
+                tmem_ld16(taddr + (uint32_t)c0, r);
+                if (row >= p.a_rows) continue;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int col = n0 + c0 + j;            // row of the BN-row operand
+                    if (col >= p.b_rows) break;
+                    const float v = __uint_as_float(r[j]);
+                    const int tok = p.swapped ? col : row, o = p.swapped ? row : col;
+                    if (p.mode == OUT_PARTIAL) {
+                        partial[((size_t)blockIdx.z * n_tok + tok) * n_out + o] = v;
+                    } else {
+                        const size_t idx = (size_t)tok * p.ld + o;
+                        if (p.out_dtype == TUFF_F32) {
+                            float* op = (float*)p.out + idx;
+                            *op = p.mode == OUT_ACCUM ? *op + v : v;
+                        } else {
+                            ((bf16*)p.out)[idx] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) {
+        // A wait ran out.  Give copies that may still be in flight time to land before the
+        // shared memory is released.
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)tmem_cols<BN>()) : "memory");
+    }
+}
+
+// Adds the split-K partial sums in split order and writes them out.
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, long long ld,
+                                     int n_tok, int n_out, int splits, int mode, int out_dtype) {
+    const size_t total = (size_t)n_tok * n_out;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * total + i];
+        const size_t t = i / n_out, o = i - t * n_out;
+        const size_t idx = t * ld + o;
+        if (out_dtype == TUFF_F32) {
+            float* op = (float*)out + idx;
+            *op = mode == OUT_ACCUM ? *op + acc : acc;
+        } else {
+            ((bf16*)out)[idx] = __float2bfloat16_rn(acc);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+PFN_cuTensorMapEncodeTiled encode_fn() {
+    static PFN_cuTensorMapEncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (PFN_cuTensorMapEncodeTiled)f;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, ld; int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        for (long long v : {k.rows, k.cols, k.ld, (long long)k.box_rows}) h = h * 1000003u ^ std::hash<long long>()(v);
+        return h;
+    }
+};
+
+// A tensor map for a K-major bf16 matrix [rows, cols] with row stride ld (elements), boxes of
+// box_rows x 64.  Maps depend on the address, so they are cached per (address, shape).
+bool tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    PFN_cuTensorMapEncodeTiled enc = encode_fn();
+    if (!enc) return false;
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estride[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return true;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_tc_kernel<BN, STAGES><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ma, mb, p);
+    return launch_status();
+}
+
+}  // namespace
+
+// Bytes of workspace that tuff_gemm_tc may need for a product with this many tokens and outputs.
+extern "C" long long tuff_gemm_tc_workspace_bytes(int m_tokens, int n_out, int k) {
+    if (m_tokens > 128) return 0;
+    const int kb = (k + BK - 1) / BK;
+    const int splits = kb < 16 ? kb : 16;
+    return (long long)splits * m_tokens * n_out * 4;
+}
+
+// C[M,N] (=|+=) A[M,K] W[N,K]^T with bf16 A and W.  C is bf16 (store only) or fp32.
+// Requirements: K % 8 == 0, lda % 8 == 0, ldw % 8 == 0, A and W 16-byte aligned (TMA strides).
+// `workspace` (fp32) is used when the K range is split; `status` is a device int that
+// receives a non-zero code if a bounded wait ran out.
+extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
+                            long long lda, long long ldw, long long ldc, int accumulate,
+                            float* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) return TUFF_E_SIZE;
+    if (accumulate && c_dtype != TUFF_F32) return TUFF_E_DTYPE;
+    if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TUFF_E_ALIGN;
+    const int k_blocks = ceil_div(K, BK);
+    const bool swapped = M <= 128;
+    GemmParams p{};
+    p.out = C; p.partial = workspace; p.status = status; p.ld = ldc; p.k_blocks = k_blocks;
+    p.out_dtype = c_dtype; p.swapped = swapped ? 1 : 0;
+    p.mode = accumulate ? OUT_ACCUM : OUT_STORE;
+    CUtensorMap ma, mb;
+    int bn, splits = 1;
+    if (swapped) {
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+        p.a_rows = N; p.b_rows = M;
+        const int tiles = ceil_div(N, BM);
+        if (tiles < 148 && k_blocks > 1) {
+            splits = ceil_div(296, tiles);
+            if (splits > 16) splits = 16;
+            if (splits > k_blocks) splits = k_blocks;
+            const long long need = (long long)splits * M * N * 4;
+            if (!workspace || need > workspace_bytes) splits = 1;
+        }
+        if (!tensor_map(&ma, W, N, K, ldw, BM) || !tensor_map(&mb, A, M, K, lda, bn)) return TUFF_E_ALIGN;
+    } else {
+        bn = N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256;
+        p.a_rows = M; p.b_rows = N;
+        if (!tensor_map(&ma, A, M, K, lda, BM) || !tensor_map(&mb, W, N, K, ldw, bn)) return TUFF_E_ALIGN;
+    }
+    p.kb_per_split = ceil_div(k_blocks, splits);
+    splits = ceil_div(k_blocks, p.kb_per_split);
+    const int user_mode = p.mode;
+    if (splits > 1) p.mode = OUT_PARTIAL;
+    dim3 grid(ceil_div(p.a_rows, BM), ceil_div(p.b_rows, bn), splits);
+    int rc;
+    switch (bn) {
+        case 16: rc = launch<16, 8>(ma, mb, p, grid, stream); break;
+        case 32: rc = launch<32, 8>(ma, mb, p, grid, stream); break;
+        case 64: rc = launch<64, 6>(ma, mb, p, grid, stream); break;
+        case 128: rc = launch<128, 5>(ma, mb, p, grid, stream); break;
+        default: rc = launch<256, 4>(ma, mb, p, grid, stream); break;
+    }
+    if (rc != 0 || splits == 1) return rc;
+    const size_t total = (size_t)M * N;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads : 148 * 8);
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(workspace, C, ldc, M, N, splits, user_mode, c_dtype);
+    return launch_status();
+}

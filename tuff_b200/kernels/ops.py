@@ -116,9 +116,83 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: 
                                c_longlong(out.stride(0)), c_int(1 if accumulate else 0), _stream()), "gemm_plain")
 
 
+_tc_state: dict = {}
+
+
+def _tc_buffers(device: torch.device, need_bytes: int):
+    """The tensor-core product's device status word and split-K workspace (grown on demand)."""
+    st = _tc_state.get(device)
+    if st is None:
+        st = _tc_state[device] = {"status": torch.zeros(1, dtype=torch.int32, device=device), "ws": None}
+    if need_bytes and (st["ws"] is None or st["ws"].numel() * 4 < need_bytes):
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the split-K workspace would have to grow inside a CUDA graph capture; "
+                              "run the step once before capturing it")
+        st["ws"] = torch.empty((need_bytes + 3) // 4, dtype=torch.float32, device=device)
+    return st
+
+
+def tc_status(device=None) -> int:
+    """The status word of the tensor-core kernels (synchronises); non-zero means a bounded wait
+    ran out: 1 producer, 2 MMA issuer, 3 epilogue."""
+    out = 0
+    for dev, st in _tc_state.items():
+        if device is None or torch.device(device) == dev:
+            out = out or int(st["status"].item())
+    return out
+
+
+def check_tc_status() -> None:
+    code = tc_status()
+    if code:
+        raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}); its results are invalid")
+
+
+def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
+    K = a.shape[1]
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+            and (out.dtype == torch.float32 or not accumulate))
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out (=|+=) a @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation)."""
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    if not gemm_tc_eligible(a, w, out, accumulate):
+        raise KernelError("gemm_tc needs bf16 operands with K, strides and addresses aligned for TMA")
+    lib = load_library("gemm_tc")
+    lib.tuff_gemm_tc_workspace_bytes.restype = c_longlong
+    need = lib.tuff_gemm_tc_workspace_bytes(c_int(M), c_int(N), c_int(K))
+    st = _tc_buffers(a.device, need)
+    ws = st["ws"]
+    _check(lib.tuff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), dtype_code(out), c_int(M), c_int(N), c_int(K),
+                            c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                            c_int(1 if accumulate else 0), _ptr(ws), c_longlong(0 if ws is None else ws.numel() * 4),
+                            _ptr(st["status"]), _stream()), "gemm_tc")
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-    """out (=|+=) a @ w.T, by the kernel that suits the element types and the shape."""
-    gemm_plain(a, w, out, accumulate)
+    """out (=|+=) a @ w.T, by the kernel that suits the element types and the shape:
+    bf16 operands that meet TMA's alignment rules go to the tensor cores, everything else
+    (the 32-bit path, odd sizes) to the plain FFMA kernel.  A bf16 activation against a
+    matrix stored in 32-bit is raised to fp32 first."""
+    if a.dtype == torch.bfloat16 and w.dtype == torch.float32:
+        a32 = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+        cast(a.contiguous(), a32)
+        if out.dtype == torch.float32:
+            gemm_plain(a32, w, out, accumulate)
+        else:
+            tmp = torch.empty(out.shape, dtype=torch.float32, device=a.device)
+            gemm_plain(a32, w, tmp, False)
+            cast(tmp, out)
+        return
+    if gemm_tc_eligible(a, w, out, accumulate):
+        gemm_tc(a, w, out, accumulate)
+    else:
+        gemm_plain(a, w, out, accumulate)
 
 
 # ------------------------------------------------------------------ short conv
