@@ -78,8 +78,9 @@ def validate_entries(entries: Sequence[StepEntry], vocab_size: int, max_context:
             raise BatchError(f"request {rid!r}: {e.cache.n_tokens} + {n} tokens exceed the context of {max_context}")
 
 
-def layout_entries(entries: Sequence[StepEntry], cache: CacheManager):
-    """Host arrays for a step (after the entries' pages were reserved)."""
+def layout_entries(entries: Sequence[StepEntry], cache: CacheManager, table_width: int | None = None):
+    """Host arrays for a step (after the entries' pages were reserved).  `table_width` fixes the
+    width of the block tables (a captured step needs the same shapes every time)."""
     R = len(entries)
     lens = [len(e.tokens) for e in entries]
     T = int(sum(lens))
@@ -100,15 +101,17 @@ def layout_entries(entries: Sequence[StepEntry], cache: CacheManager):
         want.extend(o + int(w) for w in e.want)
         o += n
     rcs = [e.cache for e in entries]
-    tables = [cache.block_table(g, rcs) for g in range(len(cache.groups))]
+    tables = [cache.block_table(g, rcs, table_width) for g in range(len(cache.groups))]
     return dict(tokens=tokens, positions=positions, row_of_token=row_of_token, cu_q=cu_q, slot_of_row=slot,
                 want_index=np.asarray(want, np.int32), block_tables=tables,
                 max_q_len=max(lens), max_seq_len=max(e.cache.n_tokens + n for e, n in zip(entries, lens)),
                 all_single=all(n == 1 for n in lens))
 
 
-def to_device(host: dict, device: torch.device, act_dtype: torch.dtype) -> StepContext:
-    """Packs the host arrays into one int32 buffer, copies it once, and cuts views."""
+def to_device(host: dict, device: torch.device, act_dtype: torch.dtype, static=None) -> StepContext:
+    """Packs the host arrays into one int32 buffer, copies it once, and cuts views.  `static`
+    = (pinned host buffer, device buffer) reuses fixed buffers, so that the views keep their
+    addresses from step to step (a captured step reads them)."""
     parts = [host["tokens"], host["positions"], host["row_of_token"], host["cu_q"], host["slot_of_row"],
              host["want_index"]] + [t.reshape(-1) for t in host["block_tables"]]
     sizes = [p.size for p in parts]
@@ -116,11 +119,23 @@ def to_device(host: dict, device: torch.device, act_dtype: torch.dtype) -> StepC
     for s in sizes:
         offs.append(total)
         total += (s + 3) // 4 * 4            # 16-byte aligned pieces
-    flat = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=torch.cuda.is_available())
+    if static is None:
+        flat = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=torch.cuda.is_available())
+    else:
+        flat = static[0]
+        assert flat.numel() >= total
+        if len(static) > 2 and static[2] is not None:
+            static[2].synchronize()          # the previous copy out of this buffer has been made
     flat_np = flat.numpy()
     for p, o in zip(parts, offs):
         flat_np[o:o + p.size] = p
-    dev = flat.to(device, non_blocking=True)
+    if static is None:
+        dev = flat.to(device, non_blocking=True)
+    else:
+        dev = static[1]
+        dev[:total].copy_(flat[:total], non_blocking=True)
+        if len(static) > 2 and static[2] is not None:
+            static[2].record()
     cut = [dev[o:o + s] for o, s in zip(offs, sizes)]
     R = host["cu_q"].size - 1
     tables = [c.view(R, -1) for c, t in zip(cut[6:], host["block_tables"])]

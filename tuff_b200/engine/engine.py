@@ -22,16 +22,19 @@ from .scheduler import Request, Scheduler, StepPlan
 
 
 class Engine:
-    def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", ctx_size: int | None = None,
+    def __init__(self, model_dir: str | None, dtype="bfloat16", device="cuda:0", ctx_size: int | None = None,
                  max_tokens: int | None = None, page_size: int = 16, max_batched_tokens: int = 2048,
-                 max_running: int = 64):
+                 max_running: int = 64, cuda_graphs: bool = True, config: dict | None = None,
+                 weight_seed: int = 0):
         """ctx_size: longest request (prompt + new tokens), the command line's -c;
         max_tokens: tokens the cache pool holds over all live requests (default: ctx_size, or
-        8192, times nothing more: one full-length request fits)."""
+        8192: one full-length request fits).  `model_dir=None` with `config` and `weight_seed`
+        builds a random-weights model on the device."""
         ctx = ctx_size or 8192
         self.runner = ModelRunner(model_dir, dtype=dtype, device=device,
                                   max_tokens=max_tokens if max_tokens is not None else ctx,
-                                  page_size=page_size, max_requests=max_running, max_context=ctx)
+                                  page_size=page_size, max_requests=max_running, max_context=ctx,
+                                  cuda_graphs=cuda_graphs, config=config, weight_seed=weight_seed)
         self.scheduler = Scheduler(self.runner.cache, max_batched_tokens=max_batched_tokens,
                                    max_running=max_running, max_context=self.runner.max_context)
         self.sampler = Sampler(self.runner.vocab_size, self.runner.device)

@@ -8,15 +8,16 @@ and :496-599 (up to eight tokens of one sequence).
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import Dict, List, Sequence
 
 import torch
 
 from ..cache.manager import CacheManager, RequestCache
 from ..cache.pool import OutOfPages
-from ..config.registry import load_config
+from ..config.registry import config_from_dict, load_config
 from ..models.model import Model
 from ..weights.loader import load_checkpoint
+from ..weights.random_init import random_device_tensors
 from .batch import BatchError, StepContext, StepEntry, layout_entries, to_device, validate_entries
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -41,16 +42,30 @@ def require_cuda(device) -> torch.device:
 
 
 class ModelRunner:
-    def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
-                 page_size: int = 16, max_requests: int = 64, max_context: int | None = None):
+    def __init__(self, model_dir: str | None, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
+                 page_size: int = 16, max_requests: int = 64, max_context: int | None = None,
+                 cuda_graphs: bool = True, config: dict | None = None, weight_seed: int = 0):
+        """`model_dir`: a folder with config.json and safetensors.  With `model_dir=None`, `config`
+        (a config.json dictionary) and `weight_seed` make a random-weights model on the device
+        without a file.  `cuda_graphs`: replay pure decode steps from captured CUDA graphs."""
         self.device = require_cuda(device)
         self.dtype = parse_dtype(dtype)
-        self.arch, self.config = load_config(model_dir)
+        if model_dir is not None:
+            self.arch, self.config = load_config(model_dir)
+        else:
+            self.arch, self.config = config_from_dict(config, "config")
         self.model = Model(self.arch.model_spec(self.config))
         with torch.cuda.device(self.device):
-            weights = load_checkpoint(model_dir, self.model.expected_tensors(), self.dtype, self.device)
+            if model_dir is not None:
+                weights = load_checkpoint(model_dir, self.model.expected_tensors(), self.dtype, self.device)
+            else:
+                weights = random_device_tensors(self.model.expected_tensors(), weight_seed, self.dtype, self.device)
             self.model.bind_weights(weights, self.dtype)
         del weights
+        self.cuda_graphs = bool(cuda_graphs)
+        self._graphs: Dict[int, dict] = {}
+        self._seen_rows: Dict[int, int] = {}
+        self.graph_replays = 0
         self.vocab_size = self.model.spec.vocab_size
         limit = self.model.spec.max_context
         self.max_context = min(x for x in (max_context, limit, 1 << 30) if x is not None)
@@ -60,6 +75,23 @@ class ModelRunner:
     # ---- requests ------------------------------------------------------------
     def open(self, request_id) -> RequestCache:
         return self.cache.open(request_id)
+
+    def synthetic_fill(self, rc: RequestCache, n_tokens: int) -> None:
+        """Makes a request hold `n_tokens` cached tokens without running them: their pages are
+        taken and keep whatever they hold.  For measurements that need a long context whose
+        content does not matter; never used by generation."""
+        self.cache.reserve(rc, n_tokens)
+        self.cache.commit(rc, n_tokens)
+
+    def randomize_cache(self, seed: int = 0) -> None:
+        """Fills every page and state with small random numbers (see `synthetic_fill`)."""
+        g = torch.Generator(device=self.device)
+        g.manual_seed(seed)
+        for st in self.cache.storages:
+            for name in ("k_pages", "v_pages", "state"):
+                t = getattr(st, name, None)
+                if t is not None:
+                    t.copy_(torch.empty(t.shape, dtype=torch.float32, device=self.device).normal_(0, 0.5, generator=g))
 
     def close(self, rc: RequestCache) -> None:
         self.cache.close(rc)
@@ -79,9 +111,53 @@ class ModelRunner:
             for e in done:
                 self.cache.cancel(e.cache)
             raise
-        with torch.cuda.device(self.device):
-            ctx = to_device(layout_entries(entries, self.cache), self.device, self.dtype)
-            logits = self.model.forward(ctx, self.cache.storages)
+        try:
+            with torch.cuda.device(self.device):
+                logits = self._run(entries)
+        except BaseException:
+            for e in entries:
+                self.cache.cancel(e.cache)
+            raise
         for e in entries:
             self.cache.commit(e.cache, len(e.tokens))
         return logits
+
+    MAX_GRAPHS = 24
+
+    def _run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        R = len(entries)
+        decode = (self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+        if not decode:
+            ctx = to_device(layout_entries(entries, self.cache), self.device, self.dtype)
+            return self.model.forward(ctx, self.cache.storages)
+        # A pure decode step: the same kernels with the same shapes every time, so it is captured
+        # once per number of rows (after one plain run that lets workspaces grow) and replayed.
+        width = (self.max_context + self.cache.page_size - 1) // self.cache.page_size
+        host = layout_entries(entries, self.cache, table_width=width)
+        host["max_seq_len"] = self.max_context            # launch shapes must not depend on the step
+        g = self._graphs.get(R)
+        if g is None:
+            self._seen_rows[R] = self._seen_rows.get(R, 0) + 1
+            if self._seen_rows[R] < 2:
+                ctx = to_device(host, self.device, self.dtype)
+                return self.model.forward(ctx, self.cache.storages)
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            n_ints = 8 * (R + 4) + len(self.cache.groups) * (R * width + 4)
+            static = (torch.empty(n_ints, dtype=torch.int32, pin_memory=True),
+                      torch.empty(n_ints, dtype=torch.int32, device=self.device), torch.cuda.Event())
+            ctx = to_device(host, self.device, self.dtype, static)
+            torch.cuda.current_stream().synchronize()
+            from ..kernels import ops
+            before = ops.LAUNCHES["n"]
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.cache.storages)
+            g = self._graphs[R] = dict(graph=graph, static=static, logits=logits, ctx=ctx,
+                                       launches=ops.LAUNCHES["n"] - before)
+            ops.LAUNCHES["n"] = before                   # captured, not run: replays are counted instead
+        else:
+            to_device(host, self.device, self.dtype, g["static"])
+        g["graph"].replay()
+        self.graph_replays += 1
+        return g["logits"]

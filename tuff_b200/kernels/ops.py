@@ -44,8 +44,12 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(status: int, what: str) -> None:
+LAUNCHES = {"n": 0}      # kernels launched through this module (a captured graph replays its share)
+
+
+def _check(status: int, what: str, kernels: int = 1) -> None:
     if status == 0:
+        LAUNCHES["n"] += kernels
         return
     if status in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[status]}")
@@ -174,6 +178,35 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
                             _ptr(st["status"]), _stream()), "gemm_tc")
 
 
+SKINNY_MAX_TOKENS = 16
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+                swiglu: bool = False) -> None:
+    """out (=|+=) a @ w.T for at most 16 tokens, streaming w once (bf16 operands).  With
+    `swiglu`, w is [2F, K] (gate rows, then up rows) and out [M, F] = silu(gate) * up."""
+    M, K = a.shape
+    N = out.shape[1]
+    assert w.shape == ((2 * N if swiglu else N), K) and out.shape[0] == M
+    if not gemm_tc_eligible(a, w, out, accumulate) or M > SKINNY_MAX_TOKENS:
+        raise KernelError("gemm_skinny needs at most 16 tokens and bf16 operands aligned to 16 bytes")
+    lib = load_library("gemm_skinny")
+    _check(lib.tuff_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), dtype_code(out), c_int(M), c_int(N), c_int(K),
+                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                c_int(1 if accumulate else 0), c_int(1 if swiglu else 0), _stream()), "gemm_skinny")
+
+
+def linear_swiglu(a: torch.Tensor, w13: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(a @ w1.T) * (a @ w3.T) for w13 = [w1; w3] stacked by rows."""
+    M, F = out.shape
+    if M <= SKINNY_MAX_TOKENS and out.dtype == torch.bfloat16 and gemm_tc_eligible(a, w13, out, False):
+        gemm_skinny(a, w13, out, swiglu=True)
+        return
+    gu = torch.empty((M, 2 * F), dtype=a.dtype, device=a.device)
+    linear(a, w13, gu)
+    swiglu(gu, out)
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (=|+=) a @ w.T, by the kernel that suits the element types and the shape:
     bf16 operands that meet TMA's alignment rules go to the tensor cores, everything else
@@ -190,7 +223,10 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
             cast(tmp, out)
         return
     if gemm_tc_eligible(a, w, out, accumulate):
-        gemm_tc(a, w, out, accumulate)
+        if a.shape[0] <= SKINNY_MAX_TOKENS:
+            gemm_skinny(a, w, out, accumulate)
+        else:
+            gemm_tc(a, w, out, accumulate)
     else:
         gemm_plain(a, w, out, accumulate)
 
@@ -210,7 +246,7 @@ def shortconv(bcx: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_o
     lib = load_library("shortconv")
     _check(lib.tuff_shortconv(_ptr(bcx), _ptr(out), dtype_code(out), _ptr(taps), _ptr(state), _ptr(slot_of_row),
                               _ptr(row_of_token), _ptr(cu_q), c_int(n), c_int(n_rows), c_int(d), c_int(K),
-                              _stream()), "shortconv")
+                              _stream()), "shortconv", kernels=2)
 
 
 # ------------------------------------------------------------------- attention

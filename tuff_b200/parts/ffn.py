@@ -27,8 +27,6 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, h, residual):
         T = h.shape[0]
-        gu = torch.empty((T, 2 * self.F), dtype=h.dtype, device=h.device)
-        ops.linear(h, self.w13, gu)
         act = torch.empty((T, self.F), dtype=h.dtype, device=h.device)
-        ops.swiglu(gu, act)
+        ops.linear_swiglu(h, self.w13, act)
         ops.linear(act, self.w2, residual, accumulate=True)

@@ -47,6 +47,31 @@ def random_tensors(expected: Dict[str, WeightDecl], seed: int,
         yield name, draw_tensor(seed, name, expected[name], store_dtype)
 
 
+def random_device_tensors(expected: Dict[str, WeightDecl], seed: int, engine_dtype: torch.dtype,
+                          device) -> Dict[str, torch.Tensor]:
+    """The random-weights mode without a file: every tensor is drawn on the device (same
+    distributions, seeded per tensor name; not the same values as the file mode's CPU draws)
+    and rounded to bfloat16 as a checkpoint would store it."""
+    out: Dict[str, torch.Tensor] = {}
+    for name in sorted(expected):
+        decl = expected[name]
+        g = torch.Generator(device=device)
+        g.manual_seed(tensor_seed(seed, name))
+        if decl.role == "table":
+            out[name] = torch.zeros(decl.shape, dtype=torch.int32, device=device)
+            continue
+        t = torch.empty(decl.shape, dtype=torch.float32, device=device)
+        if decl.init == "norm":
+            t.normal_(0.0, 0.05, generator=g).add_(1.0)
+        else:
+            t.normal_(0.0, 0.02, generator=g)
+        t = t.to(torch.bfloat16)
+        if decl.role == "vector" or engine_dtype == torch.float32:
+            t = t.to(torch.float32)
+        out[name] = t
+    return out
+
+
 def write_random_model(model_dir: str, config: Any, seed: int, store_dtype: torch.dtype = torch.bfloat16) -> str:
     """`config` is a config.json dictionary or a typed configuration of a registered architecture."""
     if isinstance(config, dict):
