@@ -149,23 +149,23 @@ def measure_decode(engine, batch, context, steps, warmup, rng, genuine_prefill):
     vocab = runner.vocab_size
     sp = SamplingParams(max_new_tokens=n_new)
     reqs = []
-    if genuine_prefill:
-        for i in range(batch):
-            reqs.append(engine.add_request(("bench", batch, i), rng.integers(0, vocab, prompt_len).tolist(), sp))
-        while any(r.n_pending() != 1 or r.cache is None for r in reqs):
-            engine.step()
-    else:
-        # long contexts whose content does not matter: pages are taken, not computed
-        from tuff_b200.engine.scheduler import RequestStatus
-        for i in range(batch):
-            r = sch.add(("bench", batch, i), rng.integers(0, vocab, prompt_len).tolist(), sp)
-            sch.waiting.remove(r)
-            r.cache = runner.open(r.request_id)
+    from tuff_b200.engine import StepEntry
+    from tuff_b200.engine.scheduler import RequestStatus
+    for i in range(batch):
+        r = sch.add(("bench", batch, i), rng.integers(0, vocab, prompt_len).tolist(), sp)
+        sch.waiting.remove(r)
+        r.cache = runner.open(r.request_id)
+        if genuine_prefill:
+            # the prompt but its last token, through the step function in portions of the token budget
+            for lo in range(0, prompt_len - 1, sch.max_batched_tokens):
+                runner.step([StepEntry(r.cache, r.prompt[lo:min(prompt_len - 1, lo + sch.max_batched_tokens)], [])])
+        else:
+            # a long context whose content does not matter: pages are taken, not computed
             runner.synthetic_fill(r.cache, prompt_len - 1)
-            r.status = RequestStatus.RUNNING
-            sch.running.append(r)
-            reqs.append(r)
-        engine.step()                                     # the last prompt token of each, for real
+        r.status = RequestStatus.RUNNING
+        sch.running.append(r)
+        reqs.append(r)
+    engine.step()                                         # the last prompt token of each: now all decode
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()

@@ -149,15 +149,17 @@ def paged_setup(rng, seqs, G, hd, page, dtype, n_pages=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("blocked", [False, True])
 @pytest.mark.parametrize("H,G,hd,page,rot", [(4, 2, 16, 4, 16), (6, 3, 48, 8, 48), (8, 1, 80, 16, 32), (2, 2, 128, 2, 0),
-                                             (5, 5, 256, 64, 256)])
-def test_qk_norm_rope_write_and_attention(dtype, H, G, hd, page, rot):
+                                             (5, 5, 256, 64, 256), (8, 2, 64, 16, 64), (6, 2, 64, 8, 64), (4, 4, 128, 32, 128),
+                                             (8, 1, 128, 64, 64), (2, 1, 64, 16, 0)])
+def test_qk_norm_rope_write_and_attention(dtype, H, G, hd, page, rot, blocked):
     """The fused q/k kernel and the paged attention together against the plain attention, for
     rows that continue at different positions; pages are scattered and other pages hold NaN."""
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(6)
     theta, eps = 12345.0, 1e-5
-    starts, lens = (0, 37, 5), (9, 1, 12)
+    starts, lens = (0, 137, 5), (9, 1, 75)       # a fresh row, a decode row deep in its context, a long portion
     seqs = [s + n for s, n in zip(starts, lens)]
     kp, vp, table = paged_setup(rng, seqs, G, hd, page, dtype)
     qn, kn = 1 + 0.1 * rng.normal(size=hd), 1 + 0.1 * rng.normal(size=hd)
@@ -172,8 +174,15 @@ def test_qk_norm_rope_write_and_attention(dtype, H, G, hd, page, rot):
         ops.qk_norm_rope_write(qkv, dev(qn), dev(kn), None if inv_freq is None else dev(inv_freq),
                                dev(pos, torch.int32), dev(rot_, torch.int32), tb, kp, vp, H, G, hd, rot, eps)
         out = torch.empty(len(pos), H * hd, dtype=DT[dtype], device="cuda")
+        per_row = [0, 0, 0]
+        for r, _, n in rows_tokens:
+            per_row[r] = n
+        cu = np.concatenate([[0], np.cumsum(per_row)])
+        # blocked: the kernel for prompt portions (rows of several tokens); else the one that takes
+        # every token by itself
         ops.paged_attention(qkv, kp, vp, tb, dev(pos, torch.int32), dev(rot_, torch.int32), out, H, G, hd,
-                            1 / math.sqrt(hd))
+                            1 / math.sqrt(hd), cu_q=dev(cu, torch.int32) if blocked else None, all_single=not blocked,
+                            max_seq_len=max(seqs))
         return out
 
     # first the earlier parts of rows 1 and 2 (their "cache"), then the step under test
@@ -199,13 +208,14 @@ def test_qk_norm_rope_write_and_attention(dtype, H, G, hd, page, rot):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_attention_finds_a_far_key_and_respects_the_window(dtype):
+@pytest.mark.parametrize("hd,blocked", [(32, False), (64, False), (64, True), (128, False)])
+def test_attention_finds_a_far_key_and_respects_the_window(dtype, hd, blocked):
     """One key among hundreds matches the query (score far above the rest): the output must be
     that key's value, wherever its page lies; with a window that ends just after it, it must not."""
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(7)
     H = G = 1
-    hd, page, n = 32, 8, 700
+    page, n = 8, 700
     kp, vp, table = paged_setup(rng, [n], G, hd, page, dtype)
     keys = rng.normal(size=(n, hd)) * 0.1
     vals = rng.normal(size=(n, hd))
@@ -219,13 +229,14 @@ def test_attention_finds_a_far_key_and_respects_the_window(dtype):
         qd = dev(q[None], DT[dtype])
         out = torch.empty(1, hd, dtype=DT[dtype], device="cuda")
         args = (qd, kp, vp, dev(table, torch.int32), dev([n - 1], torch.int32), dev([0], torch.int32), out, 1, 1, hd, 1.0)
-        ops.paged_attention(*args)
+        kw = dict(cu_q=dev([0, 1], torch.int32) if blocked else None, all_single=not blocked, max_seq_len=n)
+        ops.paged_attention(*args, **kw)
         close(out, dev(vals[far], DT[dtype]).double().cpu().numpy()[None], dtype)
         w_in, w_out = n - far, n - far - 1       # the window that just holds the key / just misses it
-        ops.paged_attention(*args, window=w_in)
+        ops.paged_attention(*args, window=w_in, **kw)
         close(out, dev(vals[far], DT[dtype]).double().cpu().numpy()[None], dtype)
         if w_out >= 1:
-            ops.paged_attention(*args, window=w_out)
+            ops.paged_attention(*args, window=w_out, **kw)
             assert (out.float().cpu().numpy() - vals[far]).std() > 0.3
 
 

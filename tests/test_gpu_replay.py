@@ -24,7 +24,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # products' inputs (activations, keys and values), layer after layer.
 TOL = {"float32": dict(atol=1e-4, rtol=1e-4), "bfloat16": dict(atol=4e-2, rtol=4e-2)}
 
-LENGTHS = {"tiny_a": (70, 45, 97, 130, 66), "tiny_b": (83, 40, 129, 65, 100), "tiny_c": (64, 33, 90, 47, 128)}
+LENGTHS = {"tiny_a": (70, 45, 97, 130, 66), "tiny_b": (83, 40, 129, 65, 100), "tiny_c": (64, 33, 90, 47, 128),
+           "tiny_d": (150, 64, 37, 193, 129)}
 
 
 @pytest.fixture(scope="module")
@@ -75,7 +76,7 @@ def test_replay_modes(models, tmp_path, name, dtype, mode):
     folder, reqs, expect = models[name]
     vocab = CONFIGS[name][0]["vocab_size"]
     steps, wanted = getattr(traces, mode)(reqs)
-    page = {"tiny_a": 16, "tiny_b": 4, "tiny_c": 8}[name]
+    page = {"tiny_a": 16, "tiny_b": 4, "tiny_c": 8, "tiny_d": 8}[name]
     runner = run_trace(folder, dtype, steps, tmp_path, page_size=page)
     compare(str(tmp_path), wanted, expect, vocab, dtype, f"{name} {mode}")
     if mode == "mixed":

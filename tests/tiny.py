@@ -26,7 +26,14 @@ TINY_C = dict(
     rope_theta=5e5, norm_eps=1e-5, conv_L_cache=2,
     layer_types=["full_attention", "conv", "full_attention"], tie_embedding=True)
 
-CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 1), "tiny_c": (TINY_C, 2)}
+# head size 64 (the tensor-core attention kernels' size) with 4 x 64 != hidden, 2 query heads per group
+TINY_D = dict(
+    architectures=["Lfm2ForCausalLM"], hidden_size=128, num_hidden_layers=5, num_attention_heads=4,
+    num_key_value_heads=2, head_dim=64, intermediate_size=320, block_auto_adjust_ff_dim=False, vocab_size=500,
+    rope_theta=1e6, norm_eps=1e-5, conv_L_cache=3,
+    layer_types=["full_attention", "conv", "full_attention", "conv", "full_attention"], tie_embedding=True)
+
+CONFIGS = {"tiny_a": (TINY_A, 0), "tiny_b": (TINY_B, 1), "tiny_c": (TINY_C, 2), "tiny_d": (TINY_D, 3)}
 
 
 def make_folder(tmp_path, name, store_dtype=None):

@@ -160,4 +160,4 @@ class ModelRunner:
             to_device(host, self.device, self.dtype, g["static"])
         g["graph"].replay()
         self.graph_replays += 1
-        return g["logits"]
+        return g["logits"].clone()        # the graph's own output is overwritten by the next replay

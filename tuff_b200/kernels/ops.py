@@ -301,8 +301,81 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
                                           c_int(window), _stream()), "paged_attention_plain")
 
 
+_attn_state: dict = {}
+
+
+def _attn_workspace(device: torch.device, n_floats: int) -> torch.Tensor | None:
+    st = _attn_state.setdefault(device, {"ws": None})
+    if n_floats and (st["ws"] is None or st["ws"].numel() < n_floats):
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("the attention workspace would have to grow inside a CUDA graph capture; "
+                              "run the step once before capturing it")
+        st["ws"] = torch.empty(n_floats, dtype=torch.float32, device=device)
+    return st["ws"] if n_floats else None
+
+
+def attention_flash_supported(q: torch.Tensor, k_pages: torch.Tensor, H: int, G: int, hd: int) -> bool:
+    if q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        return False
+    lib = load_library("attention_flash")
+    return bool(lib.tuff_attention_flash_supported(c_int(H), c_int(G), c_int(hd), c_int(k_pages.shape[2])))
+
+
+def attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
+                     window: int = 0, max_seq_len: int | None = None) -> None:
+    """Attention of a few query tokens over long cached contexts (bf16), the keys of each token cut
+    into slices that run in parallel; `max_seq_len` (an upper bound on the contexts) sizes the cut."""
+    n = q.shape[0]
+    lib = load_library("attention_flash")
+    bound = int(max_seq_len) if max_seq_len else block_table.shape[1] * k_pages.shape[2]
+    splits = lib.tuff_attention_decode_splits(c_int(n), c_int(G), c_int(max(1, bound)))
+    lib.tuff_attention_decode_workspace_floats.restype = c_longlong
+    ws = _attn_workspace(q.device, lib.tuff_attention_decode_workspace_floats(c_int(n), c_int(H), c_int(hd), c_int(splits)))
+    st = _tc_buffers(q.device, 0)
+    _check(lib.tuff_attention_decode(_ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+                                     c_longlong(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]),
+                                     _ptr(positions), _ptr(row_of_token), _ptr(out), _ptr(ws), c_int(splits),
+                                     _ptr(st["status"]), c_int(n), c_int(H), c_int(G), c_int(hd),
+                                     c_int(k_pages.shape[2]), c_float(scale), c_int(window), _stream()),
+           "attention_decode", kernels=2 if splits > 1 else 1)
+
+
+def attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
+                      window: int = 0) -> None:
+    """Causal attention of prompt portions (bf16): blocks of query tokens against the cached keys."""
+    n = q.shape[0]
+    lib = load_library("attention_flash")
+    st = _tc_buffers(q.device, 0)
+    _check(lib.tuff_attention_prefill(_ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+                                      c_longlong(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]),
+                                      _ptr(positions), _ptr(row_of_token), _ptr(cu_q), _ptr(out), _ptr(st["status"]),
+                                      c_int(n), c_int(cu_q.numel() - 1), c_int(H), c_int(G), c_int(hd),
+                                      c_int(k_pages.shape[2]), c_float(scale), c_int(window), _stream()),
+           "attention_prefill")
+
+
 def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
-                    window: int = 0, **_hints) -> None:
+                    window: int = 0, ctx=None, cu_q=None, all_single: bool | None = None,
+                    max_seq_len: int | None = None) -> None:
+    """Attention over the paged cache by the kernel that suits the batch: the tensor-core kernels
+    for bf16 with head size 64 or 128 (the sliced one when every row brings a single token, the
+    blocked one otherwise), the plain kernel for everything else."""
+    if ctx is not None:
+        cu_q = ctx.cu_q if cu_q is None else cu_q
+        all_single = ctx.all_single if all_single is None else all_single
+        max_seq_len = ctx.max_seq_len if max_seq_len is None else max_seq_len
+    assert q.stride(1) == 1 and out.shape == (q.shape[0], H * hd) and q.dtype == k_pages.dtype == out.dtype
+    if attention_flash_supported(q, k_pages, H, G, hd):
+        _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
+        _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
+        if all_single or cu_q is None:
+            attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window,
+                             max_seq_len)
+        else:
+            _i32(cu_q, "cu_q")
+            attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
+                              window)
+        return
     paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window)
 
 
