@@ -307,3 +307,78 @@ def test_temperature_sampling_follows_the_distribution():
     toks = np.array(sampler.sample(ld, [SampleRow(sp, 1, i) for i in range(n)]).tolist())
     freq = np.bincount(toks, minlength=V) / n
     assert np.abs(freq - p).max() < 4 * np.sqrt(p.max() / n) + 0.01
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 301, 80), (8, 2048, 2048), (9, 264, 96), (16, 2048, 5632), (5, 6144, 2048), (3, 40, 4096), (13, 520, 1000)])
+def test_gemm_decode_epilogues_and_fused_norm(M, N, K):
+    """The decode products: store / accumulate, with and without the RMSNorm done by the product
+    itself, against fp64 (the normed rows rounded to bf16 as the separate norm kernel stores them)."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(20)
+    w = dev(rng.normal(size=(N, K)) * 0.05, torch.bfloat16)
+    x = dev(rng.normal(size=(M, K)) * 2)
+    nw = dev(1 + 0.1 * rng.normal(size=K))
+    h = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+    ops.rmsnorm(x, nw, 1e-5, h)
+    ref = h.double().cpu().numpy() @ w.double().cpu().numpy().T
+    lazy = ops.NormedRows(x, nw, 1e-5, torch.bfloat16)
+    assert lazy.fusable(w) == (K <= ops.FUSED_NORM_MAX_K)
+    for a in (h, lazy) if lazy.fusable(w) else (h,):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.gemm_decode(a, w, out)
+        close(out, ref, "bfloat16")
+        o32 = torch.full((M, N), float("nan"), device="cuda")
+        ops.gemm_decode(a, w, o32)
+        close(o32, ref, "float32", scale=4.0)
+        res = dev(rng.normal(size=(M, N)))
+        acc = res.clone()
+        ops.gemm_decode(a, w, acc, ops.EPI_ACCUM)
+        close(acc, res.double().cpu().numpy() + ref, "float32", scale=4.0)
+    # linear() routes few-token bf16 products here, with the lazy norm too
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.linear(ops.NormedRows(x, nw, 1e-5, torch.bfloat16), w, out)
+    close(out, ref, "bfloat16")
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 100, 80), (8, 5632, 2048), (16, 264, 96), (7, 40, 64)])
+def test_gemm_decode_swiglu(M, F, K):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(21)
+    w13 = dev(rng.normal(size=(2 * F, K)) * 0.05, torch.bfloat16)
+    a = dev(rng.normal(size=(M, K)), torch.bfloat16)
+    gu = (a.double() @ w13.double().T).to(torch.bfloat16).double().cpu().numpy()
+    ref = gu[:, :F] / (1 + np.exp(-gu[:, :F])) * gu[:, F:]
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear_swiglu(a, w13, out)
+    close(out, ref, "bfloat16")
+
+
+@pytest.mark.parametrize("M,d,L", [(1, 80, 3), (8, 2048, 3), (16, 96, 4), (5, 200, 2)])
+def test_gemm_decode_shortconv(M, d, L):
+    """The input projection with the gated convolution and the state roll fused on, one token per
+    row, against the projection followed by the stand-alone convolution kernel's definition."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(22)
+    w_in = dev(rng.normal(size=(3 * d, d)) * 0.1, torch.bfloat16)
+    a = dev(rng.normal(size=(M, d)), torch.bfloat16)
+    taps = dev(rng.normal(size=(d, L)))
+    n_slots = M + 3
+    slots = rng.permutation(n_slots)[:M]
+    state0 = dev(rng.normal(size=(n_slots, L - 1, d)))
+    state = state0.clone()
+    out = torch.full((M, d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops.linear_shortconv(a, w_in, taps, state, dev(slots, torch.int32), out)
+    bcx = (a.double() @ w_in.double().T).to(torch.bfloat16).double().cpu().numpy()
+    t64, s64 = taps.double().cpu().numpy(), state0.double().cpu().numpy()
+    new = state.double().cpu().numpy()
+    for m in range(M):
+        u = bcx[m, :d] * bcx[m, 2 * d:]
+        hist = np.concatenate([s64[slots[m]], u[None]], 0)          # [L, d]
+        y = (t64.T * hist).sum(0)
+        close(out[m:m + 1], (bcx[m, d:2 * d] * y)[None], "bfloat16", scale=2.0)
+        # u = B * x from values rounded to bf16: where the kernel's fp32 sum and the fp64 product
+        # fall on different sides of a rounding boundary, u differs by a bf16 step
+        np.testing.assert_allclose(new[slots[m], -1], hist[-1], rtol=2e-2, atol=2e-2 * np.abs(hist[-1]).max())
+        np.testing.assert_array_equal(new[slots[m], :-1], s64[slots[m], 1:])       # the older entries only move
+    other = [s for s in range(n_slots) if s not in slots]
+    np.testing.assert_array_equal(new[other], s64[other])

@@ -190,7 +190,7 @@ __device__ __forceinline__ void load_tile(const CUtensorMap* mk, const CUtensorM
     const int pages = TILE / page_size;
     for (int i = 0; i < pages; ++i) {
         const int blk = tile * pages + i;
-        const int page = blk < max_blocks ? bt[blk] : -1;    // beyond the row's table: no page
+        const int page = blk < max_blocks ? ld_act(bt + blk) : -1;    // beyond the row's table: no page
         const int y = (page * G + g) * page_size;            // a missing page (-1) lies outside the tensor: zero fill
 #pragma unroll
         for (int h = 0; h < HD / 64; ++h) {
@@ -218,8 +218,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
     const int g_lane = lane >> 2, t = lane & 3;
     const int tok = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
     const int HG = p.H / p.G;
-    const int pos = p.positions[tok];
-    const int row = p.row_of_token[tok];
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DEC_STAGES; ++s) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (DEC_STAGES + s), 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_wait();                                   // everything below reads what earlier kernels wrote
+    const int pos = ld_act(p.positions + tok);
+    const int row = ld_act(p.row_of_token + tok);
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
     const int tile_lo = lo / TILE, tile_hi = pos / TILE;
     const int n_tiles = tile_hi - tile_lo + 1;
@@ -227,11 +232,6 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
     const int t_begin = tile_lo + split * per;
     const int n_local = max(0, min(per, tile_hi + 1 - t_begin));
     const int* bt = p.block_table + (size_t)row * p.max_blocks;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < DEC_STAGES; ++s) { mbar_init(bars + 8 * s, 1); mbar_init(bars + 8 * (DEC_STAGES + s), 1); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
     __syncthreads();
     bool ok = true;
     float o[Frag<HD>::DT][4];
@@ -254,8 +254,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
         const bf16* qrow = p.q + (size_t)tok * p.q_stride + (size_t)(g * HG + g_lane) * HD;
 #pragma unroll
         for (int kk = 0; kk < Frag<HD>::KS; ++kk) {
-            qa[kk][0] = g_lane < HG ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 2 * t) : 0u;
-            qa[kk][2] = g_lane < HG ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8 + 2 * t) : 0u;
+            qa[kk][0] = g_lane < HG ? ld_act_u32(qrow + 16 * kk + 2 * t) : 0u;
+            qa[kk][2] = g_lane < HG ? ld_act_u32(qrow + 16 * kk + 8 + 2 * t) : 0u;
             qa[kk][1] = 0u; qa[kk][3] = 0u;
         }
         for (int i = warp; i < n_local; i += DEC_WARPS) {
@@ -280,6 +280,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
         if (t == 0) { mine[HD] = m_a; mine[HD + 1] = l_a; }
     }
     if (!ok) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    pdl_launch_dependents();                      // the keys are read: the next kernel may start its prologue
     __syncthreads();
     // merge the warps' partial results in warp order
     for (int idx = threadIdx.x; idx < HG * HD; idx += blockDim.x) {
@@ -310,15 +311,18 @@ template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, int n_splits) {
     const size_t th = blockIdx.x;                      // token * H + head
+    pdl_wait();
+    pdl_launch_dependents();
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ld_act(ml + 2 * s));
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float L = 0.f, O = 0.f;
         for (int s = 0; s < n_splits; ++s) {
-            const float f = ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - M);
-            L += ml[2 * s + 1] * f;
-            O += part_o[(th * n_splits + s) * HD + d] * f;
+            const float ms = ld_act(ml + 2 * s);
+            const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            L += ld_act(ml + 2 * s + 1) * f;
+            O += ld_act(part_o + (th * n_splits + s) * HD + d) * f;
         }
         out[th * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
@@ -537,17 +541,17 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
         const int smem = DEC_STAGES * 2 * TILE * 64 * 2 + 128 + DEC_WARPS * 8 * (64 + 2) * 4 + 1024;
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_decode_kernel<64>, smem))) return rc; set = true; }
-        attn_decode_kernel<64><<<grid, threads, smem, stream>>>(mk, mv, p);
+        rc = launch_pdl(attn_decode_kernel<64>, grid, dim3(threads), smem, stream, mk, mv, p);
     } else {
         const int smem = DEC_STAGES * 2 * TILE * 128 * 2 + 128 + DEC_WARPS * 8 * (128 + 2) * 4 + 1024;
         static bool set = false;
         if (!set) { if ((rc = set_smem(attn_decode_kernel<128>, smem))) return rc; set = true; }
-        attn_decode_kernel<128><<<grid, threads, smem, stream>>>(mk, mv, p);
+        rc = launch_pdl(attn_decode_kernel<128>, grid, dim3(threads), smem, stream, mk, mv, p);
     }
-    if ((rc = launch_status()) || n_splits == 1) return rc;
-    if (hd == 64) attn_combine_kernel<64><<<n_tokens * H, 64, 0, stream>>>(p.part_o, p.part_ml, p.out, n_splits);
-    else attn_combine_kernel<128><<<n_tokens * H, 128, 0, stream>>>(p.part_o, p.part_ml, p.out, n_splits);
-    return launch_status();
+    if (rc || (rc = launch_status()) || n_splits == 1) return rc;
+    if (hd == 64) rc = launch_pdl(attn_combine_kernel<64>, dim3(n_tokens * H), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits);
+    else rc = launch_pdl(attn_combine_kernel<128>, dim3(n_tokens * H), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits);
+    return rc ? rc : launch_status();
 }
 
 extern "C" int tuff_attention_prefill(const void* q, long long q_stride, const void* k_pages, const void* v_pages,

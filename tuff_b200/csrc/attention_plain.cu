@@ -33,33 +33,36 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
     __shared__ float sh[QKV_WARPS][MAX_HD];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pos = positions[t];
-    const int r = row_of_token[t];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int pos = ld_act(positions + t);
+    const int r = ld_act(row_of_token + t);
     const int n_heads = H + 2 * G;
+    const int head_stride = QKV_WARPS * gridDim.y;          // heads are dealt to (block.y, warp) in turn
     const int half = rot_dim >> 1;
     T* base = qkv + (size_t)t * n_heads * hd;
     size_t page_base = 0;
     int in_page = 0;
     if (write_kv) {
-        const int page = block_table[(size_t)r * max_blocks + pos / page_size];
+        const int page = ld_act(block_table + (size_t)r * max_blocks + pos / page_size);
         in_page = pos % page_size;
         page_base = (size_t)page * G;
     }
-    for (int head = warp; head < n_heads; head += QKV_WARPS) {
+    for (int head = blockIdx.y * QKV_WARPS + warp; head < n_heads; head += head_stride) {
         T* x = base + (size_t)head * hd;
         const bool is_q = head < H, is_k = !is_q && head < H + G;
         if (!is_q && !is_k) {          // value head: copy to its page
             if (write_kv) {
                 const int g = head - H - G;
                 T* dst = v_pages + ((page_base + g) * page_size + in_page) * hd;
-                for (int e = lane; e < hd; e += 32) dst[e] = x[e];
+                for (int e = lane; e < hd; e += 32) dst[e] = from_f32<T>(ld_act(x + e));
             }
             continue;
         }
         const float* w = is_q ? q_norm_w : k_norm_w;
         float ss = 0.f;
         for (int e = lane; e < hd; e += 32) {
-            const float v = to_f32(x[e]);
+            const float v = ld_act(x + e);
             sh[warp][e] = v;
             ss = fmaf(v, v, ss);
         }
@@ -184,17 +187,20 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
     if (n_tokens <= 0) return 0;
     if (hd < 1 || hd > MAX_HD || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || G < 0 || H < 0) return TUFF_E_SIZE;
     if (write_kv && page_size < 1) return TUFF_E_SIZE;
+    // few tokens: spread a token's heads over several blocks so that the launch fills more SMs
+    const int n_heads = H + 2 * G;
+    int per_token = n_tokens >= 512 ? 1 : ceil_div(n_heads, QKV_WARPS);
+    if (per_token > 65535) per_token = 65535;
+    dim3 grid(n_tokens, per_token);
     if (dtype == TUFF_F32)
-        qk_norm_rope_write_kernel<float><<<n_tokens, QKV_WARPS * 32, 0, stream>>>(
+        return launch_pdl(qk_norm_rope_write_kernel<float>, grid, dim3(QKV_WARPS * 32), 0, stream,
             (float*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks,
             (float*)k_pages, (float*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv);
     else if (dtype == TUFF_BF16)
-        qk_norm_rope_write_kernel<bf16><<<n_tokens, QKV_WARPS * 32, 0, stream>>>(
+        return launch_pdl(qk_norm_rope_write_kernel<bf16>, grid, dim3(QKV_WARPS * 32), 0, stream,
             (bf16*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks,
             (bf16*)k_pages, (bf16*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv);
-    else
-        return TUFF_E_DTYPE;
-    return launch_status();
+    return TUFF_E_DTYPE;
 }
 
 // q: [n_tokens, H, hd] with a row stride of q_stride elements; out: [n_tokens, H*hd].

@@ -14,7 +14,9 @@ template <typename WT>
 __global__ void embed_kernel(const int* __restrict__ tokens, const WT* __restrict__ table,
                              float* __restrict__ out, int d, int vocab) {
     const int t = blockIdx.x;
-    int tok = tokens[t];
+    pdl_launch_dependents();
+    pdl_wait();
+    int tok = ld_act(tokens + t);
     const bool ok = tok >= 0 && tok < vocab;
     if (!ok) tok = 0;
     const WT* row = table + (size_t)tok * d;
@@ -27,12 +29,10 @@ extern "C" int tuff_embed(const int* tokens, const void* table, int table_dtype,
     if (n_tokens <= 0) return 0;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == TUFF_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, (const float*)table, out, d, vocab);
+        return launch_pdl(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, d, vocab);
     else if (table_dtype == TUFF_BF16)
-        embed_kernel<bf16><<<n_tokens, threads, 0, stream>>>(tokens, (const bf16*)table, out, d, vocab);
-    else
-        return TUFF_E_DTYPE;
-    return launch_status();
+        return launch_pdl(embed_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const bf16*)table, out, d, vocab);
+    return TUFF_E_DTYPE;
 }
 
 // ------------------------------------------------------------------ RMSNorm
@@ -46,25 +46,28 @@ __global__ void rmsnorm_kernel(const InT* __restrict__ x, const float* __restric
                                int d, float eps) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
-    const int src = row_index ? row_index[r] : r;
+    pdl_wait();
+    const int src = row_index ? ld_act(row_index + r) : r;
     const InT* xr = x + (size_t)src * d;
     float ss = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = to_f32(xr[i]);
+        const float v = ld_act(xr + i);
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
+    pdl_launch_dependents();
     const float scale = rsqrtf(ss / (float)d + eps);
     OutT* o = out + (size_t)r * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x)
-        o[i] = from_f32<OutT>(to_f32(xr[i]) * scale * w[i]);
+        o[i] = from_f32<OutT>(ld_act(xr + i) * scale * w[i]);
 }
 
 extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* out, int out_dtype,
                             const int* row_index, int n_rows, int d, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const int threads = 256;
-#define LAUNCH(IT, OT) rmsnorm_kernel<IT, OT><<<n_rows, threads, 0, stream>>>( \
+    int rc = 0;
+#define LAUNCH(IT, OT) rc = launch_pdl(rmsnorm_kernel<IT, OT>, dim3(n_rows), dim3(threads), 0, stream, \
         (const IT*)x, w, (OT*)out, row_index, d, eps)
     if (x_dtype == TUFF_F32 && out_dtype == TUFF_F32) LAUNCH(float, float);
     else if (x_dtype == TUFF_F32 && out_dtype == TUFF_BF16) LAUNCH(float, bf16);
@@ -72,7 +75,7 @@ extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* ou
     else if (x_dtype == TUFF_BF16 && out_dtype == TUFF_F32) LAUNCH(bf16, float);
     else return TUFF_E_DTYPE;
 #undef LAUNCH
-    return launch_status();
+    return rc ? rc : launch_status();
 }
 
 // ------------------------------------------------------------------- SwiGLU

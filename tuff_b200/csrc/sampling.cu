@@ -93,7 +93,7 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
 __device__ int block_argmax(const float* __restrict__ row, int V, float* shv, int* shi) {
     ArgMax best{-INFINITY, 0x7fffffff};
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
+        const float v = ld_act(row + i);
         if (v > best.v) { best.v = v; best.i = i; }        // ascending i: first maximum kept
     }
 #pragma unroll
@@ -119,6 +119,8 @@ argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
     __shared__ float shv[32];
     __shared__ int shi[32];
     const int r = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const int best = block_argmax(logits + (size_t)r * V, V, shv, shi);
     if (threadIdx.x == 0) out[r] = best;
 }
@@ -289,8 +291,7 @@ sample_kernel(const float* __restrict__ logits, int V, const SampleRow* __restri
 extern "C" int tuff_argmax(const float* logits, int n_rows, int V, int* out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V < 1) return TUFF_E_SIZE;
-    argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, V, out);
-    return launch_status();
+    return launch_pdl(argmax_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, V, out);
 }
 
 // rows: n_rows records of 48 bytes (see SampleRow); recent: [n_rows, max_recent]

@@ -73,15 +73,48 @@ __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restr
         st[(size_t)s * d + c] = u;
     }
 }
+
+// Every row brings exactly one token (decode): one thread per (row, channel) reads the state,
+// computes the output and rolls the state, so one launch does both steps.
+template <typename T>
+__global__ void shortconv_single_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
+                                        float* __restrict__ state, const int* __restrict__ slot_of_row,
+                                        T* __restrict__ out, int d, int K) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int r = blockIdx.x;                       // row r's token is token r
+    pdl_wait();
+    pdl_launch_dependents();
+    if (c >= d) return;
+    const T* p = bcx + (size_t)r * 3 * d;
+    const float u = ld_act(p + c) * ld_act(p + 2 * d + c);
+    float* st = state + (size_t)ld_act(slot_of_row + r) * (K - 1) * d;
+    float y = 0.f;
+    for (int j = 0; j < K - 1; ++j) {
+        const float s = ld_act(st + (size_t)j * d + c);
+        y = fmaf(taps[(size_t)c * K + j], s, y);
+        if (j > 0) st[(size_t)(j - 1) * d + c] = s;
+    }
+    y = fmaf(taps[(size_t)c * K + K - 1], u, y);
+    st[(size_t)(K - 2) * d + c] = u;
+    out[(size_t)r * d + c] = from_f32<T>(ld_act(p + d + c) * y);
+}
 }  // namespace
 
 // bcx [n_tokens, 3d], taps [d, K] fp32, state [n_slots, K-1, d] fp32, out [n_tokens, d].
 extern "C" int tuff_shortconv(const void* bcx, void* out, int dtype, const float* taps, float* state,
                               const int* slot_of_row, const int* row_of_token, const int* cu_q,
-                              int n_tokens, int n_rows, int d, int K, cudaStream_t stream) {
+                              int n_tokens, int n_rows, int d, int K, int all_single, cudaStream_t stream) {
     if (n_tokens <= 0 || n_rows <= 0) return 0;
     if (K < 2) return TUFF_E_SIZE;
     const int threads = 128;
+    if (all_single && n_tokens == n_rows) {
+        dim3 g(n_rows, ceil_div(d, threads));
+        if (dtype == TUFF_F32)
+            return launch_pdl(shortconv_single_kernel<float>, g, dim3(threads), 0, stream, (const float*)bcx, taps, state, slot_of_row, (float*)out, d, K);
+        else if (dtype == TUFF_BF16)
+            return launch_pdl(shortconv_single_kernel<bf16>, g, dim3(threads), 0, stream, (const bf16*)bcx, taps, state, slot_of_row, (bf16*)out, d, K);
+        return TUFF_E_DTYPE;
+    }
     dim3 g1(n_tokens, ceil_div(d, threads)), g2(n_rows, ceil_div(d, threads));
     if (dtype == TUFF_F32) {
         shortconv_fwd_kernel<float><<<g1, threads, 0, stream>>>((const float*)bcx, taps, state, slot_of_row,

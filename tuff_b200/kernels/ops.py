@@ -179,29 +179,74 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
 
 
 SKINNY_MAX_TOKENS = 16
+FUSED_NORM_MAX_K = 2048          # the widest row the fused RMSNorm of a decode product holds in registers
 
 
-def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
-                swiglu: bool = False) -> None:
-    """out (=|+=) a @ w.T for at most 16 tokens, streaming w once (bf16 operands).  With
-    `swiglu`, w is [2F, K] (gate rows, then up rows) and out [M, F] = silu(gate) * up."""
-    M, K = a.shape
+class NormedRows:
+    """An RMSNorm that has not run yet: `x` (fp32 [M, d]) to be normed with `weight` and `eps` into
+    `dtype`.  The decode products take it as their input and norm the rows themselves; anything
+    else calls `dense()` and gets the normed tensor (computed once)."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: torch.dtype):
+        self.x, self.weight, self.eps, self.dtype = x, weight, float(eps), dtype
+        self.shape, self.device = x.shape, x.device
+        self._dense = None
+
+    def dense(self) -> torch.Tensor:
+        if self._dense is None:
+            self._dense = torch.empty(self.x.shape, dtype=self.dtype, device=self.x.device)
+            rmsnorm(self.x, self.weight, self.eps, self._dense)
+        return self._dense
+
+    def fusable(self, w: torch.Tensor) -> bool:
+        M, K = self.x.shape
+        return (self.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS
+                and K % 8 == 0 and K <= FUSED_NORM_MAX_K and w.stride(0) % 8 == 0 and w.stride(1) == 1
+                and w.data_ptr() % 16 == 0 and self.x.is_contiguous() and self.x.data_ptr() % 16 == 0)
+
+
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_CONV = 0, 1, 2, 3
+
+
+def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, conv=None) -> None:
+    """A decode-step product for at most 16 tokens with its neighbours fused in (csrc/gemm_decode.cu):
+    `a` is a bf16 tensor [M, K] or a `NormedRows`; epilogue EPI_SWIGLU takes w = [gate; up] stacked,
+    EPI_CONV takes w = [B; C; x] stacked and conv = (taps [d, L], state [slots, L-1, d], slot_of_row)."""
+    norm = a if isinstance(a, NormedRows) else None
+    src = norm.x if norm is not None else a
+    M, K = src.shape
     N = out.shape[1]
-    assert w.shape == ((2 * N if swiglu else N), K) and out.shape[0] == M
-    if not gemm_tc_eligible(a, w, out, accumulate) or M > SKINNY_MAX_TOKENS:
-        raise KernelError("gemm_skinny needs at most 16 tokens and bf16 operands aligned to 16 bytes")
-    lib = load_library("gemm_skinny")
-    _check(lib.tuff_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), dtype_code(out), c_int(M), c_int(N), c_int(K),
-                                c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                                c_int(1 if accumulate else 0), c_int(1 if swiglu else 0), _stream()), "gemm_skinny")
+    mult = {EPI_SWIGLU: 2, EPI_CONV: 3}.get(epilogue, 1)
+    assert w.shape == (mult * N, K) and out.shape[0] == M and M <= SKINNY_MAX_TOKENS
+    taps = state = slots = None
+    L = 0
+    if epilogue == EPI_CONV:
+        taps, state, slots = conv
+        L = taps.shape[1]
+        assert taps.shape == (N, L) and state.shape[1:] == (L - 1, N) and taps.dtype == state.dtype == torch.float32
+        _i32(slots, "slot_of_row"); _contig(state, "state"); _contig(taps, "taps")
+    lib = load_library("gemm_decode")
+    _check(lib.tuff_gemm_decode(_ptr(src), _ptr(norm.weight if norm is not None else None),
+                                c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
+                                c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
+                                c_longlong(out.stride(0)), c_int(epilogue), _ptr(taps), _ptr(state), _ptr(slots),
+                                c_int(L), _stream()), "gemm_decode")
 
 
-def linear_swiglu(a: torch.Tensor, w13: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(a @ w1.T) * (a @ w3.T) for w13 = [w1; w3] stacked by rows."""
+def _decode_eligible(a, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
+    if isinstance(a, NormedRows):
+        return a.fusable(w) and out.stride(1) == 1 and (out.dtype == torch.float32 or not accumulate)
+    return a.shape[0] <= SKINNY_MAX_TOKENS and gemm_tc_eligible(a, w, out, accumulate)
+
+
+def linear_swiglu(a, w13: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(a @ w1.T) * (a @ w3.T) for w13 = [w1; w3] stacked by rows; `a` may be a NormedRows."""
     M, F = out.shape
-    if M <= SKINNY_MAX_TOKENS and out.dtype == torch.bfloat16 and gemm_tc_eligible(a, w13, out, False):
-        gemm_skinny(a, w13, out, swiglu=True)
+    if out.dtype == torch.bfloat16 and _decode_eligible(a, w13, out, False):
+        gemm_decode(a, w13, out, EPI_SWIGLU)
         return
+    if isinstance(a, NormedRows):
+        a = a.dense()
     gu = torch.empty((M, 2 * F), dtype=a.dtype, device=a.device)
     linear(a, w13, gu)
     swiglu(gu, out)
@@ -211,7 +256,13 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
     """out (=|+=) a @ w.T, by the kernel that suits the element types and the shape:
     bf16 operands that meet TMA's alignment rules go to the tensor cores, everything else
     (the 32-bit path, odd sizes) to the plain FFMA kernel.  A bf16 activation against a
-    matrix stored in 32-bit is raised to fp32 first."""
+    matrix stored in 32-bit is raised to fp32 first.  `a` may be a NormedRows (an RMSNorm still to
+    run): the decode product norms the rows itself, every other kernel gets the normed tensor."""
+    if _decode_eligible(a, w, out, accumulate):
+        gemm_decode(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
+        return
+    if isinstance(a, NormedRows):
+        a = a.dense()
     if a.dtype == torch.bfloat16 and w.dtype == torch.float32:
         a32 = torch.empty(a.shape, dtype=torch.float32, device=a.device)
         cast(a.contiguous(), a32)
@@ -223,18 +274,27 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
             cast(tmp, out)
         return
     if gemm_tc_eligible(a, w, out, accumulate):
-        if a.shape[0] <= SKINNY_MAX_TOKENS:
-            gemm_skinny(a, w, out, accumulate)
-        else:
-            gemm_tc(a, w, out, accumulate)
+        gemm_tc(a, w, out, accumulate)
     else:
         gemm_plain(a, w, out, accumulate)
 
 
+def linear_shortconv(a, w_in: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_of_row: torch.Tensor,
+                     out: torch.Tensor) -> bool:
+    """The gated short convolution of one token per row fused onto its input projection:
+    out = C * conv(B * x) with [B | C | x] = a @ w_in.T, rolling each row's state.  Returns False
+    (and does nothing) when the fused kernel does not take these tensors."""
+    if out.dtype != torch.bfloat16 or not _decode_eligible(a, w_in, out, False):
+        return False
+    gemm_decode(a, w_in, out, EPI_CONV, conv=(taps, state, slot_of_row))
+    return True
+
+
 # ------------------------------------------------------------------ short conv
 def shortconv(bcx: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_of_row: torch.Tensor,
-              row_of_token: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor) -> None:
-    """Gated short convolution of a batch of portions; rolls each row's state slot."""
+              row_of_token: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor, all_single: bool = False) -> None:
+    """Gated short convolution of a batch of portions; rolls each row's state slot.
+    `all_single`: every row brings exactly one token (one fused launch)."""
     n, d = out.shape
     K = taps.shape[1]
     assert bcx.shape == (n, 3 * d) and taps.shape == (d, K) and taps.dtype == torch.float32
@@ -246,7 +306,7 @@ def shortconv(bcx: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_o
     lib = load_library("shortconv")
     _check(lib.tuff_shortconv(_ptr(bcx), _ptr(out), dtype_code(out), _ptr(taps), _ptr(state), _ptr(slot_of_row),
                               _ptr(row_of_token), _ptr(cu_q), c_int(n), c_int(n_rows), c_int(d), c_int(K),
-                              _stream()), "shortconv", kernels=2)
+                              c_int(1 if all_single else 0), _stream()), "shortconv", kernels=1 if all_single else 2)
 
 
 # ------------------------------------------------------------------- attention

@@ -21,6 +21,8 @@ from .base import POSITION_ENCODINGS, Mixer, PagedKVNeed, PartSpec, WeightDecl, 
 
 @register_mixer("gqa_attention")
 class GQAAttention(Mixer):
+    takes_lazy_norm = True
+
     def __init__(self, d_model: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: float | None = None, position_encoding: PartSpec | dict | None = None,
                  window: int | None = None, scale: float | None = None):
@@ -59,11 +61,11 @@ class GQAAttention(Mixer):
         T = h.shape[0]
         H, G, hd = self.H, self.G, self.hd
         g_here = 0 if reads_only else G
-        qkv = torch.empty((T, (H + 2 * g_here) * hd), dtype=h.dtype, device=h.device)
+        qkv = torch.empty((T, (H + 2 * g_here) * hd), dtype=self.act_dtype, device=h.device)
         ops.linear(h, self.wq if reads_only else self.wqkv, qkv)
         table = ctx.block_tables[cache.group]
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
-        fused = self.pos.fused_tables(h.device) if (self.pos is not None and hasattr(self.pos, "fused_tables")) else None
+        fused = self.pos.fused_tables(qkv.device) if (self.pos is not None and hasattr(self.pos, "fused_tables")) else None
         if self.pos is None or fused is not None:
             inv_freq, rot = fused if fused is not None else (None, 0)
             ops.qk_norm_rope_write(qkv, self.qn, self.kn, inv_freq, ctx.positions, ctx.row_of_token, table,
@@ -79,7 +81,7 @@ class GQAAttention(Mixer):
             if not reads_only:
                 ops.qk_norm_rope_write(qkv, None, None, None, ctx.positions, ctx.row_of_token, table,
                                        cache.k_pages, cache.v_pages, H, G, hd, 0, 0.0, write_kv=True)
-        att = torch.empty((T, H * hd), dtype=h.dtype, device=h.device)
+        att = torch.empty((T, H * hd), dtype=self.act_dtype, device=qkv.device)
         ops.paged_attention(qkv, cache.k_pages, cache.v_pages, table, ctx.positions, ctx.row_of_token, att,
                             H, G, hd, self.scale, self.window or 0, ctx=ctx)
         ops.linear(att, self.wo, residual, accumulate=True)

@@ -9,7 +9,8 @@ from .base import Block, register_block
 @register_block("prenorm")
 class PreNormBlock(Block):
     def forward(self, ctx, x, layer, cache, reads_only=False):
-        h = layer.mixer_norm.forward(ctx, x)
+        # a part that says `takes_lazy_norm` may get its input as a norm still to run (ops.NormedRows)
+        h = layer.mixer_norm.forward(ctx, x, lazy=getattr(layer.mixer, "takes_lazy_norm", False))
         layer.mixer.forward(ctx, cache, h, x, reads_only)
-        h = layer.ffn_norm.forward(ctx, x)
+        h = layer.ffn_norm.forward(ctx, x, lazy=getattr(layer.ffn, "takes_lazy_norm", False))
         layer.ffn.forward(ctx, h, x)

@@ -39,6 +39,7 @@ class LMHead(Head):
         logits = torch.empty((n, self.V), dtype=torch.float32, device=x.device)
         if n == 0:
             return logits
-        h = norm.forward(ctx, x, ctx.want_index)
+        # every row wanted, in order (a decode step): the product may norm the rows itself
+        h = norm.forward(ctx, x, None if ctx.wants_all_rows else ctx.want_index, lazy=ctx.wants_all_rows)
         ops.linear(h, self.w["weight"], logits)
         return logits

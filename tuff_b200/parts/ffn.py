@@ -12,6 +12,8 @@ from .base import FeedForward, WeightDecl, register_feed_forward
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    takes_lazy_norm = True
+
     def __init__(self, d_model: int, ffn_dim: int):
         self.d, self.F = int(d_model), int(ffn_dim)
 
@@ -27,6 +29,6 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, h, residual):
         T = h.shape[0]
-        act = torch.empty((T, self.F), dtype=h.dtype, device=h.device)
+        act = torch.empty((T, self.F), dtype=self.act_dtype, device=h.device)
         ops.linear_swiglu(h, self.w13, act)
         ops.linear(act, self.w2, residual, accumulate=True)

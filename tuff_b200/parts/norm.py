@@ -17,7 +17,11 @@ class RMSNorm(Norm):
     def weight_decls(self):
         return {"weight": WeightDecl((self.dim,), role="vector", init="norm")}
 
-    def forward(self, ctx, x, row_index=None):
+    def forward(self, ctx, x, row_index=None, lazy=False):
+        """`lazy`: the caller's next step is a matrix product that can norm its own rows; it gets
+        an `ops.NormedRows` (which any other consumer turns into the tensor with `.dense()`)."""
+        if lazy and row_index is None and x.shape[0] <= ops.SKINNY_MAX_TOKENS and self.act_dtype == torch.bfloat16:
+            return ops.NormedRows(x, self.w["weight"], self.eps, self.act_dtype)
         n = x.shape[0] if row_index is None else row_index.numel()
         out = torch.empty((n, self.dim), dtype=self.act_dtype, device=x.device)
         ops.rmsnorm(x, self.w["weight"], self.eps, out, row_index)

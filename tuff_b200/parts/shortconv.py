@@ -19,6 +19,8 @@ from .base import Mixer, StateNeed, WeightDecl, register_mixer
 
 @register_mixer("gated_short_conv")
 class GatedShortConv(Mixer):
+    takes_lazy_norm = True
+
     def __init__(self, d_model: int, kernel_size: int):
         self.d, self.K = int(d_model), int(kernel_size)
         if self.K < 2:
@@ -40,8 +42,12 @@ class GatedShortConv(Mixer):
         if reads_only:
             raise ValueError("a gated_short_conv layer cannot run on another layer's state")
         T = h.shape[0]
-        bcx = torch.empty((T, 3 * self.d), dtype=h.dtype, device=h.device)
+        g = torch.empty((T, self.d), dtype=self.act_dtype, device=h.device)
+        if ctx.all_single and ops.linear_shortconv(h, self.w["in_proj"], self.taps, cache.state, ctx.slot_of_row, g):
+            ops.linear(g, self.w["out_proj"], residual, accumulate=True)
+            return
+        bcx = torch.empty((T, 3 * self.d), dtype=self.act_dtype, device=h.device)
         ops.linear(h, self.w["in_proj"], bcx)
-        g = torch.empty((T, self.d), dtype=h.dtype, device=h.device)
-        ops.shortconv(bcx, self.taps, cache.state, ctx.slot_of_row, ctx.row_of_token, ctx.cu_q, g)
+        ops.shortconv(bcx, self.taps, cache.state, ctx.slot_of_row, ctx.row_of_token, ctx.cu_q, g,
+                      all_single=ctx.all_single)
         ops.linear(g, self.w["out_proj"], residual, accumulate=True)
