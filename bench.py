@@ -228,7 +228,7 @@ def main() -> int:
     pk, pk_src = peaks()
     rng = np.random.default_rng(0)
 
-    page_size = 16
+    page_size = 64
     biggest = BATCH if args.no_points else 64
     engine = Engine(None, dtype="bfloat16", ctx_size=CONTEXT, max_tokens=biggest * CONTEXT + 4096, page_size=page_size,
                     max_batched_tokens=PREFILL_TOKENS, max_running=biggest, config=cfg_dict, weight_seed=0)

@@ -60,7 +60,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--dump-logits", metavar="PATH", help="numeric-gate mode: dump final logit vectors")
     ap.add_argument("--teacher-force", metavar="FILE", help="feed reference token IDs, report per-step top-1 agreement")
     ap.add_argument("--dtype", choices=["bfloat16", "bf16", "float32", "fp32"], default="bfloat16")
-    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--num-pages", type=int, default=None, help="cache pages (default: enough for one full context)")
     ap.add_argument("--max-batched-tokens", type=int, default=2048)
     ap.add_argument("--device", default="cuda:0")

@@ -49,12 +49,16 @@ struct GemmParams {
     int mode;             // OUT_*
     int out_dtype;        // TUFF_F32 / TUFF_BF16
     int swapped;          // 1: the 128-row operand is W, so D is [out, token]
+    int splits;           // parts the K range is cut into
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -118,18 +122,92 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int BN> constexpr int tmem_cols() { return BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256; }
+// Two accumulators of BN columns each, so that one is read out while the other is filled.
+template <int BN> constexpr int tmem_cols() { return 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512; }
 
 template <int BN, int STAGES>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
-    static constexpr int BARS = TILES;                       // full[STAGES], empty[STAGES], accum_full
-    static constexpr int TMEM_SLOT = BARS + (2 * STAGES + 1) * 8;
+    static constexpr int BARS = TILES;                       // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    static constexpr int TMEM_SLOT = BARS + (2 * STAGES + 4) * 8;
     static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;      // + room to align the base to 1024 bytes
 };
 
+// Writes 16 consecutive accumulator columns of one row: `row`/`col` index the 128-row and the
+// BN-row operand.  Not swapped: the 16 values are consecutive in the output row (vector stores
+// when aligned); swapped: they belong to 16 different tokens, and the warp's lanes hold
+// consecutive outputs, so each store of the warp is one contiguous run.
+__device__ __forceinline__ void store16(const GemmParams& p, int split, int row, int col0, const uint32_t (&r)[16]) {
+    const int n_out = p.swapped ? p.a_rows : p.b_rows;
+    const int n_tok = p.swapped ? p.b_rows : p.a_rows;
+    const int n_valid = min(16, p.b_rows - col0);
+    if (!p.swapped) {
+        if (p.mode == OUT_PARTIAL) {
+            float* dst = p.partial + ((size_t)split * n_tok + row) * n_out + col0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) if (j < n_valid) dst[j] = __uint_as_float(r[j]);
+            return;
+        }
+        const size_t idx = (size_t)row * p.ld + col0;
+        if (p.out_dtype == TUFF_BF16) {
+            bf16* dst = (bf16*)p.out + idx;
+            if (n_valid == 16 && (((uintptr_t)dst) & 15) == 0) {
+                uint32_t w[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    w[j] = *reinterpret_cast<uint32_t*>(&v);
+                }
+                reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) if (j < n_valid) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+        } else {
+            float* dst = (float*)p.out + idx;
+            if (n_valid == 16 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    if (p.mode == OUT_ACCUM) {
+                        const float4 o = reinterpret_cast<float4*>(dst)[j];
+                        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    }
+                    reinterpret_cast<float4*>(dst)[j] = v;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) if (j < n_valid) dst[j] = (p.mode == OUT_ACCUM ? dst[j] : 0.f) + __uint_as_float(r[j]);
+            }
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (j >= n_valid) break;
+        const int tok = col0 + j;
+        const float v = __uint_as_float(r[j]);
+        if (p.mode == OUT_PARTIAL) {
+            p.partial[((size_t)split * n_tok + tok) * n_out + row] = v;
+        } else {
+            const size_t idx = (size_t)tok * p.ld + row;
+            if (p.out_dtype == TUFF_F32) {
+                float* op = (float*)p.out + idx;
+                *op = p.mode == OUT_ACCUM ? *op + v : v;
+            } else {
+                ((bf16*)p.out)[idx] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
+// Persistent: each CTA walks the work items (128-row block, BN-row block, K split) that fall to
+// it, blockIdx.x, blockIdx.x + gridDim.x, ...; the 128-row block index runs fastest, so CTAs that
+// run together share the BN-row operand's tile in L2.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
@@ -141,17 +219,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t bars = base + L::BARS;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t accum_bar = bars + 8u * (2 * STAGES);
+    auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::TMEM_SLOT);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-    const int kb0 = blockIdx.z * p.kb_per_split;
-    const int nkb = min(p.kb_per_split, p.k_blocks - kb0);
+    const int mt = (p.a_rows + BM - 1) / BM, nt = (p.b_rows + BN - 1) / BN;
+    const int n_work = mt * nt * p.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -167,70 +245,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-                ok = mbar_wait(empty_bar(s), ph ^ 1u, p.status, 1);
-                if (!ok) break;
-                mbar_expect_tx(full_bar(s), L::A_BYTES + L::B_BYTES);
-                const int k = (kb0 + i) * BK;
-                tma_load_2d(a_tiles + s * L::A_BYTES, &map_a, full_bar(s), k, m0);
-                tma_load_2d(b_tiles + s * L::B_BYTES, &map_b, full_bar(s), k, n0);
+            uint32_t it = 0;                                  // k-block counter over all of this CTA's work
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+                const int m0 = (w % mt) * BM, n0 = ((w / mt) % nt) * BN, split = w / (mt * nt);
+                const int kb0 = split * p.kb_per_split;
+                const int nkb = min(p.kb_per_split, p.k_blocks - kb0);
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, p.status, 1)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(s), L::A_BYTES + L::B_BYTES);
+                    const int k = (kb0 + i) * BK;
+                    tma_load_2d(a_tiles + s * L::A_BYTES, &map_a, full_bar(s), k, m0);
+                    tma_load_2d(b_tiles + s * L::B_BYTES, &map_b, full_bar(s), k, n0);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc<BN>();
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-                ok = mbar_wait(full_bar(s), ph, p.status, 2);
-                if (!ok) break;
+            uint32_t it = 0, tile = 0;
+            for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++tile) {
+                const int split = w / (mt * nt);
+                const int nkb = min(p.kb_per_split, p.k_blocks - split * p.kb_per_split);
+                const uint32_t buf = tile & 1u;
+                // the epilogue must have emptied this accumulator (two tiles ago)
+                if (!mbar_wait(acc_empty(buf), ((tile >> 1) & 1u) ^ 1u, p.status, 4)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t a = a_tiles + s * L::A_BYTES, b = b_tiles + s * L::B_BYTES;
+                const uint32_t acc = tmem_base + buf * BN;
+                for (int i = 0; i < nkb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, p.status, 2)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a = a_tiles + s * L::A_BYTES, b = b_tiles + s * L::B_BYTES;
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k)
-                    umma(tmem_base, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
-                         (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(empty_bar(s));          // the stage is free once these MMAs have read it
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma(acc, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
+                             (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(acc_full(buf)); // the accumulator is complete once all MMAs retire
             }
-            if (ok) umma_commit(accum_bar);         // the accumulator is complete once all MMAs retire
         }
     } else {
-        ok = mbar_wait(accum_bar, 0, p.status, 3);
-        tc_fence_after();
-        if (ok) {
-            const int quad = warp & 3;                      // the 32 tensor-memory lanes this warp may read
+        const int quad = warp & 3;                          // the 32 tensor-memory lanes this warp may read
+        uint32_t tile = 0;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++tile) {
+            const int m0 = (w % mt) * BM, n0 = ((w / mt) % nt) * BN, split = w / (mt * nt);
+            const uint32_t buf = tile & 1u;
+            if (!mbar_wait(acc_full(buf), (tile >> 1) & 1u, p.status, 3)) { ok = false; break; }
+            tc_fence_after();
             const int row = m0 + quad * 32 + lane;          // row of the 128-row operand
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-            float* partial = p.partial;
-            const int n_out = p.swapped ? p.a_rows : p.b_rows;
-            const int n_tok = p.swapped ? p.b_rows : p.a_rows;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 if (n0 + c0 >= p.b_rows) break;             // uniform over the warp
                 uint32_t r[16];
                 tmem_ld16(taddr + (uint32_t)c0, r);
-                if (row >= p.a_rows) continue;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int col = n0 + c0 + j;            // row of the BN-row operand
-                    if (col >= p.b_rows) break;
-                    const float v = __uint_as_float(r[j]);
-                    const int tok = p.swapped ? col : row, o = p.swapped ? row : col;
-                    if (p.mode == OUT_PARTIAL) {
-                        partial[((size_t)blockIdx.z * n_tok + tok) * n_out + o] = v;
-                    } else {
-                        const size_t idx = (size_t)tok * p.ld + o;
-                        if (p.out_dtype == TUFF_F32) {
-                            float* op = (float*)p.out + idx;
-                            *op = p.mode == OUT_ACCUM ? *op + v : v;
-                        } else {
-                            ((bf16*)p.out)[idx] = __float2bfloat16_rn(v);
-                        }
-                    }
-                }
+                if (row < p.a_rows) store16(p, split, row, n0 + c0, r);
             }
+            // this warp has read its part of the accumulator: hand it back to the MMA thread
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
         }
     }
     if (!ok) {
@@ -381,7 +457,9 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     splits = ceil_div(k_blocks, p.kb_per_split);
     const int user_mode = p.mode;
     if (splits > 1) p.mode = OUT_PARTIAL;
-    dim3 grid(ceil_div(p.a_rows, BM), ceil_div(p.b_rows, bn), splits);
+    p.splits = splits;
+    const int n_work = ceil_div(p.a_rows, BM) * ceil_div(p.b_rows, bn) * splits;
+    dim3 grid(n_work < 148 ? n_work : 148);
     int rc;
     switch (bn) {
         case 16: rc = launch<16, 8>(ma, mb, p, grid, stream); break;

@@ -23,7 +23,7 @@ from .scheduler import Request, Scheduler, StepPlan
 
 class Engine:
     def __init__(self, model_dir: str | None, dtype="bfloat16", device="cuda:0", ctx_size: int | None = None,
-                 max_tokens: int | None = None, page_size: int = 16, max_batched_tokens: int = 2048,
+                 max_tokens: int | None = None, page_size: int = 64, max_batched_tokens: int = 2048,
                  max_running: int = 64, cuda_graphs: bool = True, config: dict | None = None,
                  weight_seed: int = 0):
         """ctx_size: longest request (prompt + new tokens), the command line's -c;

@@ -43,7 +43,7 @@ def require_cuda(device) -> torch.device:
 
 class ModelRunner:
     def __init__(self, model_dir: str | None, dtype="bfloat16", device="cuda:0", max_tokens: int = 8192,
-                 page_size: int = 16, max_requests: int = 64, max_context: int | None = None,
+                 page_size: int = 64, max_requests: int = 64, max_context: int | None = None,
                  cuda_graphs: bool = True, config: dict | None = None, weight_seed: int = 0):
         """`model_dir`: a folder with config.json and safetensors.  With `model_dir=None`, `config`
         (a config.json dictionary) and `weight_seed` make a random-weights model on the device
