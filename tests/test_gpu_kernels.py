@@ -382,3 +382,27 @@ def test_gemm_decode_shortconv(M, d, L):
         np.testing.assert_array_equal(new[slots[m], :-1], s64[slots[m], 1:])       # the older entries only move
     other = [s for s in range(n_slots) if s not in slots]
     np.testing.assert_array_equal(new[other], s64[other])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,F,K", [(3, 256, 64), (16, 640, 96), (64, 384, 128), (200, 256, 80), (2048, 5632, 256), (129, 128, 64)])
+def test_linear_swiglu_blocked_layout(dtype, M, F, K):
+    """Gate and up stacked in blocks of 128 rows: the few-token product, the tensor-core product with
+    the activation in its epilogue (more than 128 tokens) and the unfused path all give silu(g) * u."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(23)
+    w1 = dev(rng.normal(size=(F, K)) * 0.1, DT[dtype])
+    w3 = dev(rng.normal(size=(F, K)) * 0.1, DT[dtype])
+    a = dev(rng.normal(size=(M, K)), DT[dtype])
+    w13, block = ops.stack_gate_up(w1, w3)
+    assert block == 128 and w13.shape == (2 * F, K)
+    assert torch.equal(w13[:128], w1[:128]) and torch.equal(w13[128:256], w3[:128])
+    g = a.double() @ w1.double().T
+    u = a.double() @ w3.double().T
+    if dtype == "bfloat16":
+        g, u = g.to(torch.bfloat16).double(), u.to(torch.bfloat16).double()
+    ref = (g / (1 + torch.exp(-g)) * u).cpu().numpy()
+    out = torch.full((M, F), float("nan"), dtype=DT[dtype], device="cuda")
+    ops.linear_swiglu(a, w13, out, block)
+    close(out, ref, dtype, scale=2.0)
+    ops.check_tc_status()

@@ -79,27 +79,31 @@ extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* ou
 }
 
 // ------------------------------------------------------------------- SwiGLU
-// gu is [T, 2F]: gate in columns [0,F), up in columns [F,2F).
+// gu is [T, 2F]: per block of `blk` outputs, blk gate columns then blk up columns (blk = F: gate
+// in columns [0,F), up in [F,2F)).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int F) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int F, int blk) {
     const size_t total = (size_t)n_tokens * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / F;
         const int f = (int)(i - t * F);
-        const float g = to_f32(gu[t * 2 * F + f]);
-        const float u = to_f32(gu[t * 2 * F + F + f]);
+        const int gc = (f / blk) * 2 * blk + f % blk;
+        const float g = to_f32(gu[t * 2 * F + gc]);
+        const float u = to_f32(gu[t * 2 * F + gc + blk]);
         out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
-extern "C" int tuff_swiglu(const void* gu, void* out, int dtype, int n_tokens, int F, cudaStream_t stream) {
+extern "C" int tuff_swiglu(const void* gu, void* out, int dtype, int n_tokens, int F, int blk, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (blk <= 0) blk = F;
+    if (F % blk) return TUFF_E_SIZE;
     const size_t total = (size_t)n_tokens * F;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (dtype == TUFF_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, F);
-    else if (dtype == TUFF_BF16) swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, n_tokens, F);
+    if (dtype == TUFF_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, F, blk);
+    else if (dtype == TUFF_BF16) swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, n_tokens, F, blk);
     else return TUFF_E_DTYPE;
     return launch_status();
 }

@@ -36,7 +36,7 @@ constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
 constexpr uint32_t MAX_POLLS = 1u << 26;
 
-enum : int { OUT_STORE = 0, OUT_ACCUM = 1, OUT_PARTIAL = 2 };
+enum : int { OUT_STORE = 0, OUT_ACCUM = 1, OUT_PARTIAL = 2, OUT_SWIGLU = 3 };
 
 struct GemmParams {
     void* out;            // [rows_of_tokens, ld] bf16 or fp32
@@ -296,12 +296,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const int row = m0 + quad * 32 + lane;          // row of the 128-row operand
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN;
+            if (BN == 256 && p.mode == OUT_SWIGLU) {
+                // W is [gate block; up block] per 256 rows: columns c and c + 128 of the accumulator
+                // are gate and up of output column n0/2 + c.  Both are rounded to bf16 first, as a
+                // separate projection would store them.
+                bf16* orow = (bf16*)p.out + (size_t)row * p.ld + (n0 >> 1);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (n0 + c0 >= p.b_rows) break;             // uniform over the warp
-                uint32_t r[16];
-                tmem_ld16(taddr + (uint32_t)c0, r);
-                if (row < p.a_rows) store16(p, split, row, n0 + c0, r);
+                for (int c0 = 0; c0 < 128; c0 += 16) {
+                    uint32_t gq[16], uq[16];
+                    tmem_ld16(taddr + (uint32_t)c0, gq);
+                    tmem_ld16(taddr + (uint32_t)(c0 + 128), uq);
+                    if (row < p.a_rows) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            float a0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gq[2 * j])));
+                            float a1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gq[2 * j + 1])));
+                            const float u0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uq[2 * j])));
+                            const float u1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(uq[2 * j + 1])));
+                            a0 = a0 / (1.f + expf(-a0)) * u0;
+                            a1 = a1 / (1.f + expf(-a1)) * u1;
+                            __nv_bfloat162 v = __floats2bfloat162_rn(a0, a1);
+                            w[j] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        reinterpret_cast<uint4*>(orow + c0)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        reinterpret_cast<uint4*>(orow + c0)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (n0 + c0 >= p.b_rows) break;             // uniform over the warp
+                    uint32_t r[16];
+                    tmem_ld16(taddr + (uint32_t)c0, r);
+                    if (row < p.a_rows) store16(p, split, row, n0 + c0, r);
+                }
             }
             // this warp has read its part of the accumulator: hand it back to the MMA thread
             tc_fence_before();
@@ -421,11 +450,20 @@ extern "C" long long tuff_gemm_tc_workspace_bytes(int m_tokens, int n_out, int k
 // Requirements: K % 8 == 0, lda % 8 == 0, ldw % 8 == 0, A and W 16-byte aligned (TMA strides).
 // `workspace` (fp32) is used when the K range is split; `status` is a device int that
 // receives a non-zero code if a bounded wait ran out.
+// accumulate == 2: W is [2F, K] laid out as blocks of 128 gate rows followed by their 128 up rows
+// (N = 2F, a multiple of 256), and C [M, F] (bf16, ldc % 8 == 0, 16-byte aligned) receives
+// silu(gate) * up; only for M > 128.
 extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
                             long long lda, long long ldw, long long ldc, int accumulate,
                             float* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return TUFF_E_SIZE;
+    const bool swiglu = accumulate == 2;
+    if (swiglu) {
+        if (M <= 128 || (N % 256) || c_dtype != TUFF_BF16) return TUFF_E_SIZE;
+        if ((ldc % 8) || ((uintptr_t)C & 15)) return TUFF_E_ALIGN;
+        accumulate = 0;
+    }
     if (accumulate && c_dtype != TUFF_F32) return TUFF_E_DTYPE;
     if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TUFF_E_ALIGN;
     const int k_blocks = ceil_div(K, BK);
@@ -433,7 +471,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     GemmParams p{};
     p.out = C; p.partial = workspace; p.status = status; p.ld = ldc; p.k_blocks = k_blocks;
     p.out_dtype = c_dtype; p.swapped = swapped ? 1 : 0;
-    p.mode = accumulate ? OUT_ACCUM : OUT_STORE;
+    p.mode = swiglu ? OUT_SWIGLU : accumulate ? OUT_ACCUM : OUT_STORE;
     CUtensorMap ma, mb;
     int bn, splits = 1;
     if (swapped) {
@@ -449,7 +487,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         }
         if (!tensor_map(&ma, W, N, K, ldw, BM) || !tensor_map(&mb, A, M, K, lda, bn)) return TUFF_E_ALIGN;
     } else {
-        bn = N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256;
+        bn = N <= 16 ? 16 : N <= 32 ? 32 : N <= 64 ? 64 : N <= 128 ? 128 : 256;     // swiglu: N % 256 == 0, so 256
         p.a_rows = M; p.b_rows = N;
         if (!tensor_map(&ma, A, M, K, lda, BM) || !tensor_map(&mb, W, N, K, ldw, bn)) return TUFF_E_ALIGN;
     }

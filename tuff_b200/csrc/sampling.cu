@@ -125,6 +125,61 @@ argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
     if (threadIdx.x == 0) out[r] = best;
 }
 
+// Greedy choice over a wide vocabulary with few rows: the row is cut into `n_parts` pieces, one
+// block each; the block that finishes last for a row (a counter tells) merges the pieces' maxima
+// in piece order, which keeps the first maximum, and resets the counter for the next call.
+// scratch: [n_rows][n_parts] (value, index) pairs, then n_rows counters that are zero between calls.
+__global__ void __launch_bounds__(256)
+argmax_split_kernel(const float* __restrict__ logits, int V, int n_parts, float* __restrict__ part_v,
+                    int* __restrict__ part_i, unsigned* __restrict__ counters, int* __restrict__ out) {
+    __shared__ float shv[32];
+    __shared__ int shi[32];
+    __shared__ bool last;
+    const int r = blockIdx.x, part = blockIdx.y;
+    pdl_wait();
+    const int per = ((V + n_parts - 1) / n_parts + 3) & ~3;
+    const int lo = part * per, hi = min(V, lo + per);
+    const float* row = logits + (size_t)r * V;
+    ArgMax best{-INFINITY, 0x7fffffff};
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = ld_act(row + i);
+        if (v > best.v) { best.v = v; best.i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (lane == 0) { shv[warp] = best.v; shi[warp] = best.i; }
+    __syncthreads();
+    if (warp == 0) {
+        ArgMax b2{lane < nwarp ? shv[lane] : -INFINITY, lane < nwarp ? shi[lane] : 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgMax other{__shfl_xor_sync(0xffffffffu, b2.v, o), __shfl_xor_sync(0xffffffffu, b2.i, o)};
+            b2 = better(b2, other);
+        }
+        if (lane == 0) {
+            part_v[(size_t)r * n_parts + part] = b2.v;
+            part_i[(size_t)r * n_parts + part] = b2.i;
+            __threadfence();
+            last = atomicAdd(&counters[r], 1u) == (unsigned)(n_parts - 1);
+        }
+    }
+    __syncthreads();
+    if (last && threadIdx.x == 0) {
+        __threadfence();
+        ArgMax b{-INFINITY, 0x7fffffff};
+        for (int q = 0; q < n_parts; ++q) {
+            ArgMax o{__ldcg(part_v + (size_t)r * n_parts + q), __ldcg(part_i + (size_t)r * n_parts + q)};
+            b = better(b, o);
+        }
+        out[r] = b.i == 0x7fffffff ? 0 : b.i;
+        counters[r] = 0;
+    }
+}
+
 struct SampleRow {       // one per logits row, 48 bytes
     float temp, top_p, min_p, repeat_penalty;
     int top_k, n_recent;
@@ -288,9 +343,23 @@ sample_kernel(const float* __restrict__ logits, int V, const SampleRow* __restri
 }
 }  // namespace
 
-extern "C" int tuff_argmax(const float* logits, int n_rows, int V, int* out, cudaStream_t stream) {
+constexpr int ARGMAX_PARTS = 32;
+
+// Bytes of scratch that tuff_argmax wants for up to n_rows rows (it must be zero when first used).
+extern "C" long long tuff_argmax_scratch_bytes(int n_rows) { return (long long)n_rows * (ARGMAX_PARTS * 8 + 4); }
+
+// scratch: null, or tuff_argmax_scratch_bytes(n_rows) bytes, zeroed once; with it a wide row is
+// searched by several blocks.
+extern "C" int tuff_argmax(const float* logits, int n_rows, int V, int* out, void* scratch, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V < 1) return TUFF_E_SIZE;
+    if (scratch && V >= 8192 && n_rows * 4 <= 2 * 148) {
+        float* pv = (float*)scratch;
+        int* pi = (int*)(pv + (size_t)n_rows * ARGMAX_PARTS);
+        unsigned* cnt = (unsigned*)(pi + (size_t)n_rows * ARGMAX_PARTS);
+        return launch_pdl(argmax_split_kernel, dim3(n_rows, ARGMAX_PARTS), dim3(256), 0, stream, logits, V, ARGMAX_PARTS,
+                          pv, pi, cnt, out);
+    }
     return launch_pdl(argmax_kernel, dim3(n_rows), dim3(SAMPLE_THREADS), 0, stream, logits, V, out);
 }
 

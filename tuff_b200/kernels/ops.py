@@ -90,13 +90,27 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                             c_int(n), c_int(d), c_float(eps), _stream()), "rmsnorm")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate_up[:, :F]) * gate_up[:, F:]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out = silu(gate) * up.  gate_up [n, 2F] holds, per `block` outputs, block gate columns then
+    block up columns; block = 0 means all F gate columns, then all F up columns."""
     n, F = out.shape
     assert gate_up.shape == (n, 2 * F) and gate_up.dtype == out.dtype
     _contig(gate_up, "gate_up"); _contig(out, "out")
     lib = load_library("elementwise")
-    _check(lib.tuff_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out), c_int(n), c_int(F), _stream()), "swiglu")
+    _check(lib.tuff_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out), c_int(n), c_int(F), c_int(block), _stream()),
+           "swiglu")
+
+
+def stack_gate_up(w1: torch.Tensor, w3: torch.Tensor, block: int = 128):
+    """[gate; up] as one matrix for `linear_swiglu`: returns (w13, block).  When the width is a multiple
+    of `block`, the rows are laid out as `block` gate rows followed by their `block` up rows, and so on,
+    so that a 256-wide tile of the product holds matching gate and up columns; else they are stacked
+    whole (block 0)."""
+    F, K = w1.shape
+    if F % block == 0:
+        w13 = torch.stack([w1.view(F // block, block, K), w3.view(F // block, block, K)], dim=1).reshape(2 * F, K)
+        return w13.contiguous(), block
+    return torch.cat([w1, w3], dim=0).contiguous(), 0
 
 
 def cast(src: torch.Tensor, out: torch.Tensor) -> None:
@@ -160,11 +174,12 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumu
             and (out.dtype == torch.float32 or not accumulate))
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-    """out (=|+=) a @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation)."""
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, swiglu: bool = False) -> None:
+    """out (=|+=) a @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation).  `swiglu`:
+    w is a gate/up matrix in blocks of 128 (see stack_gate_up) and out [M, F] = silu(gate) * up."""
     M, K = a.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (M, N)
+    assert w.shape[1] == K and out.shape == (M, N // 2 if swiglu else N)
     if not gemm_tc_eligible(a, w, out, accumulate):
         raise KernelError("gemm_tc needs bf16 operands with K, strides and addresses aligned for TMA")
     lib = load_library("gemm_tc")
@@ -174,7 +189,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     ws = st["ws"]
     _check(lib.tuff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), dtype_code(out), c_int(M), c_int(N), c_int(K),
                             c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                            c_int(1 if accumulate else 0), _ptr(ws), c_longlong(0 if ws is None else ws.numel() * 4),
+                            c_int(2 if swiglu else 1 if accumulate else 0), _ptr(ws),
+                            c_longlong(0 if ws is None else ws.numel() * 4),
                             _ptr(st["status"]), _stream()), "gemm_tc")
 
 
@@ -208,7 +224,7 @@ class NormedRows:
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_CONV = 0, 1, 2, 3
 
 
-def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, conv=None) -> None:
+def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, conv=None, set_block: int = 0) -> None:
     """A decode-step product for at most 16 tokens with its neighbours fused in (csrc/gemm_decode.cu):
     `a` is a bf16 tensor [M, K] or a `NormedRows`; epilogue EPI_SWIGLU takes w = [gate; up] stacked,
     EPI_CONV takes w = [B; C; x] stacked and conv = (taps [d, L], state [slots, L-1, d], slot_of_row)."""
@@ -230,7 +246,7 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
                                 c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
                                 c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
                                 c_longlong(out.stride(0)), c_int(epilogue), _ptr(taps), _ptr(state), _ptr(slots),
-                                c_int(L), _stream()), "gemm_decode")
+                                c_int(L), c_int(set_block), _stream()), "gemm_decode")
 
 
 def _decode_eligible(a, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
@@ -239,17 +255,24 @@ def _decode_eligible(a, w: torch.Tensor, out: torch.Tensor, accumulate: bool) ->
     return a.shape[0] <= SKINNY_MAX_TOKENS and gemm_tc_eligible(a, w, out, accumulate)
 
 
-def linear_swiglu(a, w13: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(a @ w1.T) * (a @ w3.T) for w13 = [w1; w3] stacked by rows; `a` may be a NormedRows."""
+def linear_swiglu(a, w13: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out = silu(a @ w1.T) * (a @ w3.T) for (w13, block) = stack_gate_up(w1, w3); `a` may be a
+    NormedRows.  Few tokens: the decode product with the activation as its epilogue; many tokens and
+    the blocked layout: the tensor-core product with the activation as its epilogue; else the product,
+    then the activation kernel."""
     M, F = out.shape
     if out.dtype == torch.bfloat16 and _decode_eligible(a, w13, out, False):
-        gemm_decode(a, w13, out, EPI_SWIGLU)
+        gemm_decode(a, w13, out, EPI_SWIGLU, set_block=block)
         return
     if isinstance(a, NormedRows):
         a = a.dense()
+    if (block == 128 and M > 128 and out.dtype == torch.bfloat16 and gemm_tc_eligible(a, w13, out, False)
+            and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0):
+        gemm_tc(a, w13, out, swiglu=True)
+        return
     gu = torch.empty((M, 2 * F), dtype=a.dtype, device=a.device)
     linear(a, w13, gu)
-    swiglu(gu, out)
+    swiglu(gu, out, block)
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
@@ -444,12 +467,22 @@ SAMPLE_ROW_FORMAT = "<ffffiiQQQ"     # temp, top_p, min_p, repeat_penalty, top_k
 SAMPLE_ROW_BYTES = struct.calcsize(SAMPLE_ROW_FORMAT)
 
 
+_argmax_scratch: dict = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = index of the first maximum of logits[r]."""
     n, V = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == n
     _contig(logits, "logits")
     lib = load_library("sampling")
-    _check(lib.tuff_argmax(_ptr(logits), c_int(n), c_int(V), _ptr(out), _stream()), "argmax")
+    lib.tuff_argmax_scratch_bytes.restype = c_longlong
+    key = (logits.device, n)
+    scratch = _argmax_scratch.get(key)
+    if scratch is None and not torch.cuda.is_current_stream_capturing():
+        scratch = _argmax_scratch[key] = torch.zeros(lib.tuff_argmax_scratch_bytes(c_int(n)), dtype=torch.uint8,
+                                                     device=logits.device)
+    _check(lib.tuff_argmax(_ptr(logits), c_int(n), c_int(V), _ptr(out), _ptr(scratch), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, rows: torch.Tensor, recent: torch.Tensor | None, work: torch.Tensor,
