@@ -48,6 +48,14 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
         in_page = pos % page_size;
         page_base = (size_t)page * G;
     }
+    // the rotation of element e depends on the token's position and on e alone: once per token
+    float rc[MAX_HD / 32], rs[MAX_HD / 32];
+#pragma unroll
+    for (int i = 0; i < MAX_HD / 32; ++i) {
+        const int e = lane + 32 * i;
+        rc[i] = 1.f; rs[i] = 0.f;
+        if (e < rot_dim) sincosf((float)pos * inv_freq[e < half ? e : e - half], &rs[i], &rc[i]);
+    }
     for (int head = blockIdx.y * QKV_WARPS + warp; head < n_heads; head += head_stride) {
         T* x = base + (size_t)head * hd;
         const bool is_q = head < H, is_k = !is_q && head < H + G;
@@ -77,14 +85,14 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
             if (!write_kv) dst = nullptr;
             else dst = k_pages + ((page_base + (head - H)) * page_size + in_page) * hd;
         }
-        for (int e = lane; e < hd; e += 32) {
+#pragma unroll
+        for (int i = 0; i < MAX_HD / 32; ++i) {
+            const int e = lane + 32 * i;
+            if (e >= hd) break;
             float v = sh[warp][e];
             if (e < rot_dim) {
-                const int j = e < half ? e : e - half;
-                float sn, cs;
-                sincosf((float)pos * inv_freq[j], &sn, &cs);
-                v = e < half ? v * cs - sh[warp][e + half] * sn
-                             : sh[warp][e - half] * sn + v * cs;
+                v = e < half ? v * rc[i] - sh[warp][e + half] * rs[i]
+                             : sh[warp][e - half] * rs[i] + v * rc[i];
             }
             if (is_q) x[e] = from_f32<T>(v);
             else {

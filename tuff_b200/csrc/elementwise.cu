@@ -62,9 +62,66 @@ __global__ void rmsnorm_kernel(const InT* __restrict__ x, const float* __restric
         o[i] = from_f32<OutT>(ld_act(xr + i) * scale * w[i]);
 }
 
+// Many rows (prompt portions): one warp per row, eight rows per block.  A lane loads its share
+// of the row as float4 (all loads in flight at once), keeps it in registers for the scaling, and
+// writes packed output; no block-wide barrier.  Rows of up to 32 * 4 * RMS_VEC columns.
+constexpr int RMS_VEC = 16;
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ out,
+                    const int* __restrict__ row_index, int n_rows, int d, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + warp;
+    pdl_wait();
+    if (r >= n_rows) return;
+    const int src = row_index ? ld_act(row_index + r) : r;
+    const float* xr = x + (size_t)src * d;
+    float4 v[RMS_VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int k = (i * 32 + lane) * 4;
+        if (k < d) v[i] = __ldcg(reinterpret_cast<const float4*>(xr + k));
+    }
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int k = (i * 32 + lane) * 4;
+        if (k < d) {
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    const float scale = rsqrtf(ss / (float)d + eps);
+    OutT* o = out + (size_t)r * d;
+#pragma unroll
+    for (int i = 0; i < RMS_VEC; ++i) {
+        const int k = (i * 32 + lane) * 4;
+        if (k < d) {
+            const float4 g = *reinterpret_cast<const float4*>(w + k);
+            const float a = v[i].x * scale * g.x, b = v[i].y * scale * g.y, c = v[i].z * scale * g.z, e = v[i].w * scale * g.w;
+            if (sizeof(OutT) == 2) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+                *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(o) + k) =
+                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            } else {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + k) = make_float4(a, b, c, e);
+            }
+        }
+    }
+}
+
 extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* out, int out_dtype,
                             const int* row_index, int n_rows, int d, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (x_dtype == TUFF_F32 && n_rows >= 64 && d % 4 == 0 && d <= 128 * RMS_VEC && !((uintptr_t)x & 15) &&
+        !((uintptr_t)w & 15) && !((uintptr_t)out & 15)) {
+        const dim3 grid(ceil_div(n_rows, 8));
+        if (out_dtype == TUFF_BF16)
+            return launch_pdl(rmsnorm_rows_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)x, w, (bf16*)out, row_index, n_rows, d, eps);
+        if (out_dtype == TUFF_F32)
+            return launch_pdl(rmsnorm_rows_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, w, (float*)out, row_index, n_rows, d, eps);
+    }
     const int threads = 256;
     int rc = 0;
 #define LAUNCH(IT, OT) rc = launch_pdl(rmsnorm_kernel<IT, OT>, dim3(n_rows), dim3(threads), 0, stream, \

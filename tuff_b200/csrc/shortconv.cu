@@ -47,6 +47,55 @@ __global__ void shortconv_fwd_kernel(const T* __restrict__ bcx, const float* __r
     out[(size_t)t * d + c] = from_f32<T>(to_f32(bcx[(size_t)t * ld + d + c]) * y);
 }
 
+// bf16, d % 8 == 0: a thread takes 8 neighbouring channels of one token with 16-byte loads.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__global__ void shortconv_fwd_vec_kernel(const bf16* __restrict__ bcx, const float* __restrict__ taps,
+                                         const float* __restrict__ state, const int* __restrict__ slot_of_row,
+                                         const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
+                                         bf16* __restrict__ out, int n_tokens, int d, int K) {
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    const int t = blockIdx.x;
+    if (c >= d) return;
+    const int r = row_of_token[t];
+    const int i = t - cu_q[r];
+    const size_t ld = (size_t)3 * d;
+    const float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int back = (K - 1) - j;
+        float u[8];
+        if (i - back >= 0) {
+            const bf16* p = bcx + (size_t)(t - back) * ld;
+            float b[8], x[8];
+            unpack8(*reinterpret_cast<const uint4*>(p + c), b);
+            unpack8(*reinterpret_cast<const uint4*>(p + 2 * d + c), x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) u[e] = b[e] * x[e];
+        } else {
+            const float* sp = st + (size_t)((K - 1) + (i - back)) * d + c;
+            const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+            u[0] = s0.x; u[1] = s0.y; u[2] = s0.z; u[3] = s0.w; u[4] = s1.x; u[5] = s1.y; u[6] = s1.z; u[7] = s1.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = fmaf(taps[(size_t)(c + e) * K + j], u[e], y[e]);
+    }
+    float g[8];
+    unpack8(*reinterpret_cast<const uint4*>(bcx + (size_t)t * ld + d + c), g);
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(g[2 * e] * y[2 * e], g[2 * e + 1] * y[2 * e + 1]);
+        w[e] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * d + c) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // New state entry s (0 = oldest) is u at portion index n-(K-1)+s; if that is
 // negative it is the old entry s+n.  Ascending s reads old entries before they
 // are overwritten, since s+n > s.
@@ -121,8 +170,12 @@ extern "C" int tuff_shortconv(const void* bcx, void* out, int dtype, const float
                                                                  row_of_token, cu_q, (float*)out, n_tokens, d, K);
         shortconv_state_kernel<float><<<g2, threads, 0, stream>>>((const float*)bcx, state, slot_of_row, cu_q, d, K);
     } else if (dtype == TUFF_BF16) {
-        shortconv_fwd_kernel<bf16><<<g1, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row,
-                                                                row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
+        if (d % 8 == 0 && !((uintptr_t)bcx & 15) && !((uintptr_t)out & 15) && !((uintptr_t)state & 15))
+            shortconv_fwd_vec_kernel<<<dim3(n_tokens, ceil_div(d / 8, threads)), threads, 0, stream>>>(
+                (const bf16*)bcx, taps, state, slot_of_row, row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
+        else
+            shortconv_fwd_kernel<bf16><<<g1, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row,
+                                                                    row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
         shortconv_state_kernel<bf16><<<g2, threads, 0, stream>>>((const bf16*)bcx, state, slot_of_row, cu_q, d, K);
     } else {
         return TUFF_E_DTYPE;
