@@ -132,7 +132,8 @@ struct SmemLayout {
     static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
     static constexpr int BARS = TILES;                       // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     static constexpr int TMEM_SLOT = BARS + (2 * STAGES + 4) * 8;
-    static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;      // + room to align the base to 1024 bytes
+    static constexpr int OUT_STAGE = TMEM_SLOT + 16;         // 4 epilogue warps x 2 KB, 16-byte aligned
+    static constexpr int TOTAL = OUT_STAGE + 4 * 2048 + 1024;   // + room to align the base to 1024 bytes
 };
 
 // Writes 16 consecutive accumulator columns of one row: `row`/`col` index the 128-row and the
@@ -203,6 +204,64 @@ __device__ __forceinline__ void store16(const GemmParams& p, int split, int row,
             }
         }
     }
+}
+
+// The same 16 columns of 32 rows (one epilogue warp's rows), written so that every store of the warp
+// covers whole 32-byte sectors: the warp's values go through a 2 KB staging tile in shared memory
+// (16-byte slots XOR-swizzled by the row so that neither side has bank conflicts), and come back
+// with four lanes per row (fp32) or two lanes per row (bf16).  Only for a full, aligned chunk of
+// the unswapped form; every lane of the warp must call it.
+// Residual values (fp32 out, OUT_ACCUM) that store16_rows will add for the chunk at col0: loaded
+// ahead of time so that their latency is not paid chunk by chunk.
+__device__ __forceinline__ void load_residual(const GemmParams& p, int row0, int col0, int lane, float4 (&o)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int rr = (lane >> 2) + 8 * i;
+        o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p.mode == OUT_ACCUM && row0 + rr < p.a_rows)
+            o[i] = *(reinterpret_cast<const float4*>((const float*)p.out + (size_t)(row0 + rr) * p.ld + col0) + (lane & 3));
+    }
+}
+
+__device__ __forceinline__ void store16_rows(const GemmParams& p, uint8_t* stage, int row0, int col0, int lane,
+                                             const uint32_t (&r)[16], const float4 (&o)[4]) {
+    if (p.out_dtype == TUFF_F32) {
+        uint4* st = reinterpret_cast<uint4*>(stage);                    // [32 rows][4 slots]
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st[lane * 4 + (q ^ sw)] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        __syncwarp();
+        const int c4 = lane & 3;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rr = (lane >> 2) + 8 * i;
+            const uint4 u = st[rr * 4 + (c4 ^ ((rr >> 1) & 3))];
+            if (row0 + rr < p.a_rows)
+                *(reinterpret_cast<float4*>((float*)p.out + (size_t)(row0 + rr) * p.ld + col0) + c4) =
+                    make_float4(__uint_as_float(u.x) + o[i].x, __uint_as_float(u.y) + o[i].y,
+                                __uint_as_float(u.z) + o[i].z, __uint_as_float(u.w) + o[i].w);
+        }
+    } else {
+        uint4* st = reinterpret_cast<uint4*>(stage);                    // [32 rows][2 slots]
+        uint32_t w[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            w[j] = *reinterpret_cast<uint32_t*>(&v);
+        }
+        const int sw = (lane >> 2) & 1;
+        st[lane * 2 + (0 ^ sw)] = make_uint4(w[0], w[1], w[2], w[3]);
+        st[lane * 2 + (1 ^ sw)] = make_uint4(w[4], w[5], w[6], w[7]);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int rr = (lane >> 1) + 16 * i, h = lane & 1;
+            const uint4 u = st[rr * 2 + (h ^ ((rr >> 2) & 1))];
+            if (row0 + rr < p.a_rows)
+                *(reinterpret_cast<uint4*>((bf16*)p.out + (size_t)(row0 + rr) * p.ld + col0) + h) = u;
+        }
+    }
+    __syncwarp();
 }
 
 // Persistent: each CTA walks the work items (128-row block, BN-row block, K split) that fall to
@@ -324,12 +383,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             } else {
+                // whole, aligned chunks of the unswapped form go out as full sectors through shared memory
+                const int esz = p.out_dtype == TUFF_F32 ? 4 : 2;
+                const bool rows_ok = !p.swapped && p.mode != OUT_PARTIAL && ((p.ld * esz) % 16 == 0) &&
+                                     ((((uintptr_t)p.out) + (size_t)n0 * esz) % 16 == 0);
+                uint8_t* stage = base_ptr + L::OUT_STAGE + (warp - 2) * 2048;
+                const bool resid = rows_ok && p.mode == OUT_ACCUM && p.out_dtype == TUFF_F32;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (n0 + c0 >= p.b_rows) break;             // uniform over the warp
-                    uint32_t r[16];
-                    tmem_ld16(taddr + (uint32_t)c0, r);
-                    if (row < p.a_rows) store16(p, split, row, n0 + c0, r);
+                for (int g0 = 0; g0 < BN; g0 += 64) {
+                    if (n0 + g0 >= p.b_rows) break;             // uniform over the warp
+                    // the residual values of up to four chunks, all in flight at once
+                    float4 o[4][4];
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int c0 = g0 + cc * 16;
+                        if (resid && c0 < BN && n0 + c0 + 16 <= p.b_rows) load_residual(p, m0 + quad * 32, n0 + c0, lane, o[cc]);
+                        else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) o[cc][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    }
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int c0 = g0 + cc * 16;
+                        if (c0 >= BN || n0 + c0 >= p.b_rows) break;
+                        uint32_t r[16];
+                        tmem_ld16(taddr + (uint32_t)c0, r);
+                        if (rows_ok && n0 + c0 + 16 <= p.b_rows) store16_rows(p, stage, m0 + quad * 32, n0 + c0, lane, r, o[cc]);
+                        else if (row < p.a_rows) store16(p, split, row, n0 + c0, r);
+                    }
                 }
             }
             // this warp has read its part of the accumulator: hand it back to the MMA thread
