@@ -505,9 +505,23 @@ extern "C" int tuff_attention_flash_supported(int H, int G, int hd, int page_siz
 // needs (partial outputs, then maxima and sums).
 extern "C" int tuff_attention_decode_splits(int n_tokens, int G, int max_seq_len) {
     const int tiles = (max_seq_len + TILE - 1) / TILE;
-    int want = (2 * 148 + n_tokens * G - 1) / (n_tokens * G);
+    if (const char* e = getenv("TUFF_ATTN_SPLITS")) { const int v = atoi(e); if (v > 0) return v < tiles ? v : tiles; }
+    // Enough CTAs to cover the SMs twice; beyond what stays resident at once (three CTAs per SM),
+    // a count that fills whole rounds: a last round that is nearly empty costs a full round.
+    const int pairs = n_tokens * G, resident = 3 * 148;
+    int want = (2 * 148 + pairs - 1) / pairs;
+    if (pairs * want > resident) {
+        int best = want;
+        double best_eff = 0.0;
+        for (int s = want; s <= want + 1; ++s) {
+            const int ctas = pairs * s, rounds = (ctas + resident - 1) / resident;
+            const double eff = (double)ctas / ((double)rounds * resident);
+            if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+        }
+        want = best;
+    }
     if (want > tiles) want = tiles;
-    if (want > 32) want = 32;
+    if (want > 16) want = 16;          // more slices than this only add merge work
     return want < 1 ? 1 : want;
 }
 extern "C" long long tuff_attention_decode_workspace_floats(int n_tokens, int H, int hd, int n_splits) {
