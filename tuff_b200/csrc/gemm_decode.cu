@@ -64,10 +64,12 @@ __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(_
 // boundaries, are always in flight in a ring of registers: a block is refilled as soon as it has
 // been used, before the item's partial sums are added up, so the stream from HBM never drains.
 template <int NG, int D, bool HI, bool NORM, int EPI, typename CT>
-__device__ __forceinline__ void decode_op(const DecodeGemm& p, uint8_t* smem) {
+__global__ void __launch_bounds__(WARPS * 32, 2)
+gemm_decode_kernel(DecodeGemm p) {
     constexpr int B = 2;                                                      // blocks in flight per lane
     constexpr int SETS = EPI == EPI_SWIGLU ? 2 : EPI == EPI_CONV ? 3 : 1;     // row sets that are combined
     constexpr int GPS = NG / SETS;                                            // groups per set
+    extern __shared__ __align__(16) uint8_t smem[];
     float* red = reinterpret_cast<float*>(smem);                       // [WARPS][NG][16][8]
     bf16* hs = reinterpret_cast<bf16*>(smem + WARPS * NG * 128 * 4);    // NORM: [M_pad][K + 8] bf16
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,6 +86,7 @@ __device__ __forceinline__ void decode_op(const DecodeGemm& p, uint8_t* smem) {
     const bool lo_ok = g < p.M, hi_ok = HI && (g + 8 < p.M);
     const int hs_ld = K + 8;                                   // padded row of the normed activations
 
+    pdl_wait();
     if (NORM) {
         // RMSNorm of the M residual rows into shared memory as bf16, once per CTA.  All 256 threads
         // share each row: a thread holds one float4 of every row of a half (8 rows) per 1024 columns,
@@ -270,74 +273,7 @@ __device__ __forceinline__ void decode_op(const DecodeGemm& p, uint8_t* smem) {
             __syncthreads();                                     // `red` is reused by the next item
         }
     }
-}
-
-template <int NG, int D, bool HI, bool NORM, int EPI, typename CT>
-__global__ void __launch_bounds__(WARPS * 32, 2)
-gemm_decode_kernel(DecodeGemm p) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    pdl_wait();
-    decode_op<NG, D, HI, NORM, EPI, CT>(p, smem);
     pdl_launch_dependents();
-}
-
-// ---------------------------------------------------------------------------- chains
-// Several decode products in one launch: the CTAs stay, run product after product, and meet at a
-// grid-wide barrier between two products (the next one reads what this one wrote).  A launch, its
-// ramp and its drain are paid once per chain instead of once per product.  The launch is
-// cooperative, so all CTAs are resident and the barrier cannot starve; its wait is bounded all the
-// same and records a code in *status if it runs out.
-constexpr int MAX_CHAIN = 20;
-
-enum : int { V_STORE_BF16 = 0, V_STORE_F32, V_ACCUM, V_SWIGLU, V_CONV, V_STORE_BF16_WIDE, V_STORE_F32_WIDE, V_COUNT };
-
-struct Chain {
-    DecodeGemm op[MAX_CHAIN];
-    unsigned char variant[MAX_CHAIN];
-    unsigned char norm[MAX_CHAIN];
-    int n;
-    unsigned* counter;       // zero at launch
-    int* status;
-};
-
-__device__ __forceinline__ void grid_barrier(unsigned* counter, unsigned target, int* status) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(counter, 1u);
-        unsigned spins = 0;
-        while (*reinterpret_cast<volatile unsigned*>(counter) < target) {
-            if (++spins > (1u << 24)) { atomicCAS(status, 0, 31); break; }
-            __nanosleep(32);
-        }
-        __threadfence();
-    }
-    __syncthreads();
-}
-
-template <bool HI, bool NORM>
-__device__ __forceinline__ void chain_op(const DecodeGemm& p, int variant, uint8_t* smem) {
-    switch (variant) {
-        case V_STORE_BF16: decode_op<1, 4, HI, NORM, EPI_STORE, bf16>(p, smem); break;
-        case V_STORE_F32: decode_op<1, 4, HI, NORM, EPI_STORE, float>(p, smem); break;
-        case V_STORE_BF16_WIDE: decode_op<2, 4, HI, NORM, EPI_STORE, bf16>(p, smem); break;
-        case V_STORE_F32_WIDE: decode_op<2, 4, HI, NORM, EPI_STORE, float>(p, smem); break;
-        case V_ACCUM: decode_op<1, 4, HI, NORM, EPI_ACCUM, float>(p, smem); break;
-        case V_SWIGLU: decode_op<2, 4, HI, NORM, EPI_SWIGLU, bf16>(p, smem); break;
-        default: decode_op<3, 2, HI, NORM, EPI_CONV, bf16>(p, smem); break;
-    }
-}
-
-template <bool HI>
-__global__ void __launch_bounds__(WARPS * 32, 2)
-gemm_decode_chain_kernel(const __grid_constant__ Chain c) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    pdl_wait();
-    for (int i = 0; i < c.n; ++i) {
-        if (c.norm[i]) chain_op<HI, true>(c.op[i], c.variant[i], smem);
-        else chain_op<HI, false>(c.op[i], c.variant[i], smem);
-        if (i + 1 < c.n) grid_barrier(c.counter, (unsigned)(i + 1) * gridDim.x, c.status);
-    }
 }
 
 template <int NG, int D, bool NORM, int EPI, typename CT>
@@ -366,72 +302,7 @@ int launch(const DecodeGemm& p, cudaStream_t stream) {
     return launch_pdl(k, grid, dim3(WARPS * 32), smem, stream, p);
 }
 
-
-// ---- host side of the chains: while recording is on, tuff_gemm_decode queues instead of launching
-bool g_recording = false;
-Chain g_chain;
-
-int variant_of(int epilogue, int c_dtype, int N) {
-    const bool wide = ceil_div(N, 16) >= 2 * 148;
-    if (epilogue == EPI_SWIGLU) return V_SWIGLU;
-    if (epilogue == EPI_CONV) return V_CONV;
-    if (epilogue == EPI_ACCUM) return V_ACCUM;
-    if (c_dtype == TUFF_BF16) return wide ? V_STORE_BF16_WIDE : V_STORE_BF16;
-    return wide ? V_STORE_F32_WIDE : V_STORE_F32;
-}
-
-size_t chain_smem(const Chain& c) {
-    size_t most = 0;
-    for (int i = 0; i < c.n; ++i) {
-        const int ng = c.variant[i] == V_CONV ? 3 : (c.variant[i] == V_SWIGLU || c.variant[i] >= V_STORE_BF16_WIDE) ? 2 : 1;
-        const int m_pad = c.op[i].M > 8 ? 16 : 8;
-        const size_t s = (size_t)WARPS * ng * 128 * 4 + (c.norm[i] ? (size_t)m_pad * (c.op[i].K + 8) * 2 : 0);
-        most = s > most ? s : most;
-    }
-    return most;
-}
-
-template <bool HI>
-int launch_chain(const Chain& c, cudaStream_t stream) {
-    auto k = gemm_decode_chain_kernel<HI>;
-    const size_t smem = chain_smem(c);
-    cudaError_t e;
-    if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
-        return (int)e;
-    int per_sm = 0, dev = 0, sms = 0;
-    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, WARPS * 32, smem)) != cudaSuccess) return (int)e;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (per_sm < 1) return TUFF_E_SIZE;
-    if (per_sm > 2) per_sm = 2;
-    if ((e = cudaMemsetAsync(c.counter, 0, sizeof(unsigned), stream)) != cudaSuccess) return (int)e;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(per_sm * sms); cfg.blockDim = dim3(WARPS * 32); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, k, c);
-}
 }  // namespace
-
-// While recording is on, tuff_gemm_decode appends its product to a chain instead of launching it;
-// tuff_gemm_decode_chain_flush launches the recorded products as one kernel (in order, a grid-wide
-// barrier between two) and leaves recording as it was.  counter: one device word; status: the
-// device word that receives a code if the barrier's bounded wait runs out.
-extern "C" void tuff_gemm_decode_chain_record(int on) { g_recording = on != 0; if (!on) g_chain.n = 0; }
-extern "C" int tuff_gemm_decode_chain_pending() { return g_chain.n; }
-extern "C" int tuff_gemm_decode_chain_capacity() { return MAX_CHAIN; }
-
-extern "C" int tuff_gemm_decode_chain_flush(unsigned* counter, int* status, cudaStream_t stream) {
-    if (g_chain.n == 0) return 0;
-    g_chain.counter = counter; g_chain.status = status;
-    bool hi = false;
-    for (int i = 0; i < g_chain.n; ++i) hi = hi || g_chain.op[i].M > 8;
-    const int rc = hi ? launch_chain<true>(g_chain, stream) : launch_chain<false>(g_chain, stream);
-    g_chain.n = 0;
-    return rc ? rc : launch_status();
-}
 
 // epilogue: 0 store, 1 add into fp32 C, 2 swiglu (W is [2N, K]: gate rows then up rows), 3 gated
 // short convolution (W is [3N, K]: B, C, x rows; one token per row of A; taps [N, L], state
@@ -459,14 +330,6 @@ extern "C" int tuff_gemm_decode(const void* A, const float* norm_w, float eps, c
     p.set_block = set_block ? set_block : N;
     p.M = M; p.N = N; p.K = K; p.eps = eps; p.taps = taps; p.state = state; p.slot_of_row = slot_of_row; p.L = L;
     const bool norm = norm_w != nullptr;
-    if (g_recording) {
-        if (g_chain.n >= MAX_CHAIN) return TUFF_E_SIZE;          // the caller flushes before the chain is full
-        g_chain.op[g_chain.n] = p;
-        g_chain.variant[g_chain.n] = (unsigned char)variant_of(epilogue, c_dtype, N);
-        g_chain.norm[g_chain.n] = norm ? 1 : 0;
-        ++g_chain.n;
-        return 0;
-    }
 #define PICK(NGV, DV, EPI, CT) (norm ? launch<NGV, DV, true, EPI, CT>(p, stream) : launch<NGV, DV, false, EPI, CT>(p, stream))
     // two groups of 8 columns per item when that still leaves every resident CTA an item
     const bool wide = ceil_div(N, 16) >= 2 * 148;

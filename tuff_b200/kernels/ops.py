@@ -8,7 +8,6 @@ raises (`tuff_b200.kernels.build.KernelBuildError`).
 from __future__ import annotations
 
 import ctypes
-import os
 import struct
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -48,47 +47,6 @@ def _stream() -> c_void_p:
 LAUNCHES = {"n": 0}      # kernels launched through this module (a captured graph replays its share)
 
 
-# ---- chains of decode products -------------------------------------------------------------
-# While a chain is open, `gemm_decode` queues its product instead of launching it; the queue is
-# launched as one kernel (`flush_chain`) as soon as any other kernel of this module is about to
-# run, when it is full, or when the chain is closed.  Code that touches the products' tensors by
-# other means (torch operations) must call `flush_chain()` first.
-_chain = {"open": False, "keep": [], "counter": None}
-
-
-def chain_begin() -> None:
-    if _chain["open"]:
-        return
-    lib = load_library("gemm_decode")
-    lib.tuff_gemm_decode_chain_record(c_int(1))
-    _chain["open"] = True
-
-
-def flush_chain() -> None:
-    if not _chain["open"] or not _chain["keep"]:
-        return
-    lib = load_library("gemm_decode")
-    dev = _chain["keep"][0][0].device
-    if _chain["counter"] is None or _chain["counter"].device != dev:
-        _chain["counter"] = torch.zeros(1, dtype=torch.int32, device=dev)
-    st = _tc_buffers(dev, 0)
-    n = lib.tuff_gemm_decode_chain_pending()
-    status = lib.tuff_gemm_decode_chain_flush(_ptr(_chain["counter"]), _ptr(st["status"]), _stream())
-    _chain["keep"].clear()
-    _check(status, "gemm_decode chain", kernels=1 if n else 0)
-
-
-def chain_end() -> None:
-    if not _chain["open"]:
-        return
-    try:
-        flush_chain()
-    finally:
-        load_library("gemm_decode").tuff_gemm_decode_chain_record(c_int(0))
-        _chain["open"] = False
-        _chain["keep"].clear()
-
-
 def _check(status: int, what: str, kernels: int = 1) -> None:
     if status == 0:
         LAUNCHES["n"] += kernels
@@ -111,7 +69,6 @@ def _i32(t: torch.Tensor | None, name: str) -> None:
 # ----------------------------------------------------------------- elementwise
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, :] = table[tokens[t], :] as float32."""
-    flush_chain()
     _i32(tokens, "tokens")
     n, d = out.shape
     assert out.dtype == torch.float32 and table.shape[1] == d and tokens.numel() == n
@@ -124,7 +81,6 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             row_index: torch.Tensor | None = None) -> None:
     """out[r] = x[row_index[r] or r] * rsqrt(mean(x^2) + eps) * weight."""
-    flush_chain()
     d = x.shape[-1]
     n = out.shape[0]
     assert weight.dtype == torch.float32 and weight.numel() == d and out.shape[-1] == d
@@ -137,7 +93,6 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     """out = silu(gate) * up.  gate_up [n, 2F] holds, per `block` outputs, block gate columns then
     block up columns; block = 0 means all F gate columns, then all F up columns."""
-    flush_chain()
     n, F = out.shape
     assert gate_up.shape == (n, 2 * F) and gate_up.dtype == out.dtype
     _contig(gate_up, "gate_up"); _contig(out, "out")
@@ -159,7 +114,6 @@ def stack_gate_up(w1: torch.Tensor, w3: torch.Tensor, block: int = 128):
 
 
 def cast(src: torch.Tensor, out: torch.Tensor) -> None:
-    flush_chain()
     assert src.numel() == out.numel()
     _contig(src, "src"); _contig(out, "out")
     lib = load_library("elementwise")
@@ -170,7 +124,6 @@ def cast(src: torch.Tensor, out: torch.Tensor) -> None:
 # ------------------------------------------------------------------------ GEMM
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (=|+=) a @ w.T with fp32 FFMA accumulation; a [M,K], w [N,K], out [M,N]."""
-    flush_chain()
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.shape == (M, N)
@@ -224,7 +177,6 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumu
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, swiglu: bool = False) -> None:
     """out (=|+=) a @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation).  `swiglu`:
     w is a gate/up matrix in blocks of 128 (see stack_gate_up) and out [M, F] = silu(gate) * up."""
-    flush_chain()
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.shape == (M, N // 2 if swiglu else N)
@@ -243,11 +195,6 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
 
 
 SKINNY_MAX_TOKENS = 16
-# Decode products as chains (one cooperative launch for several, grid barriers between them).  Off
-# unless TUFF_CHAINS=1: measured 1.53 ms a decode step against 1.31 ms with one launch per product,
-# because a barrier costs about what a launch costs and the fixed grid balances items worse; it pays
-# only once the next product's weights are prefetched across the barrier.
-CHAINS_ENABLED = os.environ.get("TUFF_CHAINS", "0") == "1"
 FUSED_NORM_MAX_K = 2048          # the widest row the fused RMSNorm of a decode product holds in registers
 
 
@@ -299,11 +246,7 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
                                 c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
                                 c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
                                 c_longlong(out.stride(0)), c_int(epilogue), _ptr(taps), _ptr(state), _ptr(slots),
-                                c_int(L), c_int(set_block), _stream()), "gemm_decode", kernels=0 if _chain["open"] else 1)
-    if _chain["open"]:
-        _chain["keep"].append((src, w, out, norm, taps, state, slots))
-        if lib.tuff_gemm_decode_chain_pending() >= lib.tuff_gemm_decode_chain_capacity():
-            flush_chain()
+                                c_int(L), c_int(set_block), _stream()), "gemm_decode")
 
 
 def _decode_eligible(a, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
@@ -375,7 +318,6 @@ def shortconv(bcx: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_o
               row_of_token: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor, all_single: bool = False) -> None:
     """Gated short convolution of a batch of portions; rolls each row's state slot.
     `all_single`: every row brings exactly one token (one fused launch)."""
-    flush_chain()
     n, d = out.shape
     K = taps.shape[1]
     assert bcx.shape == (n, 3 * d) and taps.shape == (d, K) and taps.dtype == torch.float32
@@ -400,7 +342,6 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
 
     k_pages / v_pages: [num_pages, G, page_size, hd]; block_table: [rows, max_blocks] int32.
     """
-    flush_chain()
     n = qkv.shape[0]
     assert qkv.shape[1] == (H + 2 * G) * hd
     _contig(qkv, "qkv"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
@@ -431,7 +372,6 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
 
     q: [n, >= H*hd] (row stride taken from the tensor), out: [n, H*hd].
     """
-    flush_chain()
     n = q.shape[0]
     assert q.stride(1) == 1 and out.shape == (n, H * hd) and q.dtype == k_pages.dtype == out.dtype
     _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
@@ -468,7 +408,6 @@ def attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, 
                      window: int = 0, max_seq_len: int | None = None) -> None:
     """Attention of a few query tokens over long cached contexts (bf16), the keys of each token cut
     into slices that run in parallel; `max_seq_len` (an upper bound on the contexts) sizes the cut."""
-    flush_chain()
     n = q.shape[0]
     lib = load_library("attention_flash")
     bound = int(max_seq_len) if max_seq_len else block_table.shape[1] * k_pages.shape[2]
@@ -487,7 +426,6 @@ def attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, 
 def attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
                       window: int = 0) -> None:
     """Causal attention of prompt portions (bf16): blocks of query tokens against the cached keys."""
-    flush_chain()
     n = q.shape[0]
     lib = load_library("attention_flash")
     st = _tc_buffers(q.device, 0)
@@ -534,7 +472,6 @@ _argmax_scratch: dict = {}
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     """out[r] = index of the first maximum of logits[r]."""
-    flush_chain()
     n, V = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == n
     _contig(logits, "logits")
@@ -551,7 +488,6 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
 def sample(logits: torch.Tensor, rows: torch.Tensor, recent: torch.Tensor | None, work: torch.Tensor,
            out: torch.Tensor) -> None:
     """Samples one token per logits row; `rows` holds packed SAMPLE_ROW_FORMAT records (uint8 tensor)."""
-    flush_chain()
     n, V = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == n
     assert rows.dtype == torch.uint8 and rows.numel() == n * SAMPLE_ROW_BYTES

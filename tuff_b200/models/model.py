@@ -85,18 +85,8 @@ class Model:
     # ---- one step ----------------------------------------------------------
     def forward(self, ctx, storages) -> torch.Tensor:
         """Runs the tokens of `ctx` through the schedule; returns fp32 logits [n_wanted, vocab]."""
-        from ..kernels import ops
-        # few tokens in bf16: consecutive decode products run as chains, one launch each
-        chained = ctx.act_dtype == torch.bfloat16 and ctx.n_tokens <= ops.SKINNY_MAX_TOKENS and ops.CHAINS_ENABLED
-        if chained:
-            ops.chain_begin()
-        try:
-            x = self.embedding.forward(ctx)
-            for e in self.schedule:
-                layer = self.layers[e.layer]
-                layer.block.forward(ctx, x, layer, storages[e.storage], e.reads_only)
-            logits = self.head.forward(ctx, x, self.final_norm)
-        finally:
-            if chained:
-                ops.chain_end()
-        return logits
+        x = self.embedding.forward(ctx)
+        for e in self.schedule:
+            layer = self.layers[e.layer]
+            layer.block.forward(ctx, x, layer, storages[e.storage], e.reads_only)
+        return self.head.forward(ctx, x, self.final_norm)

@@ -22,7 +22,6 @@ from .base import POSITION_ENCODINGS, Mixer, PagedKVNeed, PartSpec, WeightDecl, 
 @register_mixer("gqa_attention")
 class GQAAttention(Mixer):
     takes_lazy_norm = True
-    ops_only = True            # touches tensors through tuff_b200.kernels.ops alone
 
     def __init__(self, d_model: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm_eps: float | None = None, position_encoding: PartSpec | dict | None = None,

@@ -3,21 +3,14 @@ x += ffn(norm_b(x)), the residual stream staying in fp32 throughout
 (reference: src/lfm25_engine.c:365-423)."""
 from __future__ import annotations
 
-from ..kernels import ops
 from .base import Block, register_block
 
 
 @register_block("prenorm")
 class PreNormBlock(Block):
     def forward(self, ctx, x, layer, cache, reads_only=False):
-        # a part that says `takes_lazy_norm` may get its input as a norm still to run (ops.NormedRows);
-        # a part that does not say `ops_only` may touch tensors with other means than tuff_b200's
-        # kernels, so queued decode products are launched before it runs
-        if not getattr(layer.mixer, "ops_only", False):
-            ops.flush_chain()
+        # a part that says `takes_lazy_norm` may get its input as a norm still to run (ops.NormedRows)
         h = layer.mixer_norm.forward(ctx, x, lazy=getattr(layer.mixer, "takes_lazy_norm", False))
         layer.mixer.forward(ctx, cache, h, x, reads_only)
-        if not getattr(layer.ffn, "ops_only", False):
-            ops.flush_chain()
         h = layer.ffn_norm.forward(ctx, x, lazy=getattr(layer.ffn, "takes_lazy_norm", False))
         layer.ffn.forward(ctx, h, x)

@@ -15,7 +15,6 @@ from .base import FeedForward, WeightDecl, register_feed_forward
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     takes_lazy_norm = True
-    ops_only = True            # touches tensors through tuff_b200.kernels.ops alone
 
     def __init__(self, d_model: int, ffn_dim: int):
         self.d, self.F = int(d_model), int(ffn_dim)

@@ -20,7 +20,6 @@ from .base import Mixer, StateNeed, WeightDecl, register_mixer
 @register_mixer("gated_short_conv")
 class GatedShortConv(Mixer):
     takes_lazy_norm = True
-    ops_only = True            # touches tensors through tuff_b200.kernels.ops alone
 
     def __init__(self, d_model: int, kernel_size: int):
         self.d, self.K = int(d_model), int(kernel_size)
