@@ -40,7 +40,14 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current CUDA stream of the current device as a raw handle (the fast path skips the
+    construction of a torch.cuda.Stream object, which costs more than the launch itself)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
