@@ -22,6 +22,10 @@ namespace {
 constexpr int MAX_HD = 256;
 constexpr int QKV_WARPS = 4;
 
+// One warp per head at a time.  A lane owns element pairs: pair j < rot_dim/2 is the rotation pair
+// (j, j + rot_dim/2); the pairs after those cover the unrotated rest of the head two by two.  So the
+// norm needs one warp reduction and the rotation no exchange between lanes; a warp works on
+// several heads at once (independent loads), since it is latency that limits this kernel.
 template <typename T>
 __global__ void __launch_bounds__(QKV_WARPS * 32)
 qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_w,
@@ -30,7 +34,8 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
                           const int* __restrict__ block_table, int max_blocks,
                           T* __restrict__ k_pages, T* __restrict__ v_pages,
                           int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv) {
-    __shared__ float sh[QKV_WARPS][MAX_HD];
+    constexpr int PPL = MAX_HD / 64;                 // pairs per lane
+    constexpr int UNROLL = 4;                        // heads in flight per warp
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_wait();
@@ -38,8 +43,7 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
     const int pos = ld_act(positions + t);
     const int r = ld_act(row_of_token + t);
     const int n_heads = H + 2 * G;
-    const int head_stride = QKV_WARPS * gridDim.y;          // heads are dealt to (block.y, warp) in turn
-    const int half = rot_dim >> 1;
+    const int half = rot_dim >> 1, n_pairs = hd >> 1;
     T* base = qkv + (size_t)t * n_heads * hd;
     size_t page_base = 0;
     int in_page = 0;
@@ -48,59 +52,71 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
         in_page = pos % page_size;
         page_base = (size_t)page * G;
     }
-    // the rotation of element e depends on the token's position and on e alone: once per token
-    float rc[MAX_HD / 32], rs[MAX_HD / 32];
+    // this lane's pairs: element indices and rotation
+    int e1[PPL], e2[PPL];
+    float rc[PPL], rs[PPL], wq1[PPL], wq2[PPL], wk1[PPL], wk2[PPL];
 #pragma unroll
-    for (int i = 0; i < MAX_HD / 32; ++i) {
-        const int e = lane + 32 * i;
+    for (int i = 0; i < PPL; ++i) {
+        const int j = lane + 32 * i;
+        e1[i] = j < half ? j : rot_dim + 2 * (j - half);
+        e2[i] = j < half ? j + half : e1[i] + 1;
         rc[i] = 1.f; rs[i] = 0.f;
-        if (e < rot_dim) sincosf((float)pos * inv_freq[e < half ? e : e - half], &rs[i], &rc[i]);
+        if (j < half) sincosf((float)pos * inv_freq[j], &rs[i], &rc[i]);
+        const bool ok = j < n_pairs;
+        wq1[i] = (ok && q_norm_w) ? q_norm_w[e1[i]] : 1.f; wq2[i] = (ok && q_norm_w) ? q_norm_w[e2[i]] : 1.f;
+        wk1[i] = (ok && k_norm_w) ? k_norm_w[e1[i]] : 1.f; wk2[i] = (ok && k_norm_w) ? k_norm_w[e2[i]] : 1.f;
     }
-    for (int head = blockIdx.y * QKV_WARPS + warp; head < n_heads; head += head_stride) {
-        T* x = base + (size_t)head * hd;
-        const bool is_q = head < H, is_k = !is_q && head < H + G;
-        if (!is_q && !is_k) {          // value head: copy to its page
-            if (write_kv) {
-                const int g = head - H - G;
-                T* dst = v_pages + ((page_base + g) * page_size + in_page) * hd;
-                for (int e = lane; e < hd; e += 32) dst[e] = from_f32<T>(ld_act(x + e));
+    // heads are dealt to (block.y, warp) in turn, UNROLL at a time
+    const int stride = QKV_WARPS * gridDim.y;
+    for (int h0 = blockIdx.y * QKV_WARPS + warp; h0 < n_heads; h0 += stride * UNROLL) {
+        float a[UNROLL][PPL], b[UNROLL][PPL], ss[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int head = h0 + u * stride;
+            ss[u] = 0.f;
+#pragma unroll
+            for (int i = 0; i < PPL; ++i) {
+                const bool ok = head < n_heads && lane + 32 * i < n_pairs;
+                a[u][i] = ok ? ld_act(base + (size_t)head * hd + e1[i]) : 0.f;
+                b[u][i] = ok ? ld_act(base + (size_t)head * hd + e2[i]) : 0.f;
             }
-            continue;
-        }
-        const float* w = is_q ? q_norm_w : k_norm_w;
-        float ss = 0.f;
-        for (int e = lane; e < hd; e += 32) {
-            const float v = ld_act(x + e);
-            sh[warp][e] = v;
-            ss = fmaf(v, v, ss);
-        }
-        ss = warp_sum(ss);
-        const float scale = w ? rsqrtf(ss / (float)hd + eps) : 1.f;
-        __syncwarp();
-        if (w)
-            for (int e = lane; e < hd; e += 32) sh[warp][e] = sh[warp][e] * scale * w[e];
-        __syncwarp();
-        T* dst = x;
-        if (is_k) {
-            if (!write_kv) dst = nullptr;
-            else dst = k_pages + ((page_base + (head - H)) * page_size + in_page) * hd;
         }
 #pragma unroll
-        for (int i = 0; i < MAX_HD / 32; ++i) {
-            const int e = lane + 32 * i;
-            if (e >= hd) break;
-            float v = sh[warp][e];
-            if (e < rot_dim) {
-                v = e < half ? v * rc[i] - sh[warp][e + half] * rs[i]
-                             : sh[warp][e - half] * rs[i] + v * rc[i];
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int i = 0; i < PPL; ++i) ss[u] = fmaf(a[u][i], a[u][i], fmaf(b[u][i], b[u][i], ss[u]));
+            ss[u] = warp_sum(ss[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int head = h0 + u * stride;
+            if (head >= n_heads) break;
+            const bool is_q = head < H, is_k = !is_q && head < H + G;
+            T* x = base + (size_t)head * hd;
+            if (!is_q && !is_k) {          // value head: copy to its page
+                if (write_kv) {
+                    T* dst = v_pages + ((page_base + (head - H - G)) * page_size + in_page) * hd;
+#pragma unroll
+                    for (int i = 0; i < PPL; ++i)
+                        if (lane + 32 * i < n_pairs) { dst[e1[i]] = from_f32<T>(a[u][i]); dst[e2[i]] = from_f32<T>(b[u][i]); }
+                }
+                continue;
             }
-            if (is_q) x[e] = from_f32<T>(v);
-            else {
-                if (dst) dst[e] = from_f32<T>(v);
-                x[e] = from_f32<T>(v);
+            const bool normed = is_q ? q_norm_w != nullptr : k_norm_w != nullptr;
+            const float scale = normed ? rsqrtf(ss[u] / (float)hd + eps) : 1.f;
+            T* dst = (is_k && write_kv) ? k_pages + ((page_base + (head - H)) * page_size + in_page) * hd : nullptr;
+#pragma unroll
+            for (int i = 0; i < PPL; ++i) {
+                if (lane + 32 * i >= n_pairs) break;
+                const float v1 = a[u][i] * scale * (is_q ? wq1[i] : wk1[i]);
+                const float v2 = b[u][i] * scale * (is_q ? wq2[i] : wk2[i]);
+                const float o1 = v1 * rc[i] - v2 * rs[i];          // identity for the unrotated pairs
+                const float o2 = v1 * rs[i] + v2 * rc[i];
+                x[e1[i]] = from_f32<T>(o1);
+                x[e2[i]] = from_f32<T>(o2);
+                if (dst) { dst[e1[i]] = from_f32<T>(o1); dst[e2[i]] = from_f32<T>(o2); }
             }
         }
-        __syncwarp();
     }
 }
 
@@ -193,7 +209,7 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
                                        int n_tokens, int H, int G, int hd, int rot_dim, int page_size,
                                        float eps, int write_kv, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (hd < 1 || hd > MAX_HD || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || G < 0 || H < 0) return TUFF_E_SIZE;
+    if (hd < 2 || hd > MAX_HD || (hd & 1) || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || G < 0 || H < 0) return TUFF_E_SIZE;
     if (write_kv && page_size < 1) return TUFF_E_SIZE;
     // few tokens: spread a token's heads over several blocks so that the launch fills more SMs
     const int n_heads = H + 2 * G;
