@@ -26,7 +26,8 @@ constexpr int QKV_WARPS = 4;
 // (j, j + rot_dim/2); the pairs after those cover the unrotated rest of the head two by two.  So the
 // norm needs one warp reduction and the rotation no exchange between lanes; a warp works on
 // several heads at once (independent loads), since it is latency that limits this kernel.
-template <typename T>
+// PPL: element pairs per lane (head size <= 64 * PPL).
+template <typename T, int PPL>
 __global__ void __launch_bounds__(QKV_WARPS * 32)
 qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_w,
                           const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
@@ -34,7 +35,6 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
                           const int* __restrict__ block_table, int max_blocks,
                           T* __restrict__ k_pages, T* __restrict__ v_pages,
                           int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv) {
-    constexpr int PPL = MAX_HD / 64;                 // pairs per lane
     constexpr int UNROLL = 4;                        // heads in flight per warp
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -216,14 +216,15 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
     int per_token = n_tokens >= 512 ? 1 : ceil_div(n_heads, QKV_WARPS);
     if (per_token > 65535) per_token = 65535;
     dim3 grid(n_tokens, per_token);
-    if (dtype == TUFF_F32)
-        return launch_pdl(qk_norm_rope_write_kernel<float>, grid, dim3(QKV_WARPS * 32), 0, stream,
-            (float*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks,
-            (float*)k_pages, (float*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv);
-    else if (dtype == TUFF_BF16)
-        return launch_pdl(qk_norm_rope_write_kernel<bf16>, grid, dim3(QKV_WARPS * 32), 0, stream,
-            (bf16*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks,
-            (bf16*)k_pages, (bf16*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv);
+#define QK_GO(T, PPL) return launch_pdl(qk_norm_rope_write_kernel<T, PPL>, grid, dim3(QKV_WARPS * 32), 0, stream, \
+        (T*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks, \
+        (T*)k_pages, (T*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv)
+    if (dtype == TUFF_F32) {
+        if (hd <= 64) QK_GO(float, 1); else if (hd <= 128) QK_GO(float, 2); else QK_GO(float, 4);
+    } else if (dtype == TUFF_BF16) {
+        if (hd <= 64) QK_GO(bf16, 1); else if (hd <= 128) QK_GO(bf16, 2); else QK_GO(bf16, 4);
+    }
+#undef QK_GO
     return TUFF_E_DTYPE;
 }
 
