@@ -347,7 +347,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
     const int n_cons = HG * QB;                   // consumer warps that take part
     const int QTOK = 16 * QB;
     // which row and which block of its tokens is this CTA's?
-    int row = -1, blk = blockIdx.x, q0 = 0, q1 = 0;
+    // later blocks of a row see more keys: they are started first, so the long ones do not trail
+    int row = -1, blk = (int)gridDim.x - 1 - (int)blockIdx.x, q0 = 0, q1 = 0;
     for (int r = 0; r < p.n_rows; ++r) {
         const int a = p.cu_q[r], b = p.cu_q[r + 1];
         const int nb = (b - a + QTOK - 1) / QTOK;
