@@ -333,7 +333,7 @@ constexpr int PRE_WARPS = 8;
 constexpr int PRE_STAGES = 3;
 
 template <int HD>
-__global__ void __launch_bounds__((PRE_WARPS + 1) * 32)
+__global__ void __launch_bounds__((PRE_WARPS + 1) * 32, HD <= 64 ? 2 : 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv, AttnParams p) {
     constexpr int STAGE_BYTES = 2 * TILE * HD * 2;
     extern __shared__ uint8_t smem_raw[];
