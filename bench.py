@@ -14,7 +14,7 @@ printed at the end holds
   roofline   bytes the decode step has to read (every weight once, the live requests' keys and
              values and states) over its time, against the measured copy bandwidth,
   points     decode tokens a second at batch 1 and 64 (same context).
-Peaks come from MEASURED_PEAKS.json when the driver wrote it, else the fallback figures.
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else the fallback figures.
 For more than one GPU it prints one line that says so and exits with 2: the engine is
 single-GPU.  `--impl reference` answers that the reference cannot run here.
 """

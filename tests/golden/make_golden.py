@@ -73,7 +73,9 @@ def main():
     import gguf
     from plain_lfm2 import read_safetensors
     from tuff_b200.weights import write_random_model
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/a/checkout/of/niihelium/tuff")
+    ref_root = sys.argv[1]
     script = os.path.join(ref_root, "tools", "lfm25_fp64_ref.py")
     out = {}
     for name, case in CASES.items():

@@ -62,7 +62,8 @@ __global__ void rmsnorm_kernel(const InT* __restrict__ x, const float* __restric
         o[i] = from_f32<OutT>(ld_act(xr + i) * scale * w[i]);
 }
 
-// Many rows (prompt portions): one warp per row, eight rows per block.  A lane loads its share
+// More than a handful of rows: one warp per row, one to eight rows per block (fewer rows, smaller blocks, so
+// that they spread over the SMs).  A lane loads its share
 // of the row as float4 (all loads in flight at once), keeps it in registers for the scaling, and
 // writes packed output; no block-wide barrier.  Rows of up to 32 * 4 * RMS_VEC columns.
 constexpr int RMS_VEC = 16;
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ out,
                     const int* __restrict__ row_index, int n_rows, int d, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = blockIdx.x * 8 + warp;
+    const int r = blockIdx.x * (blockDim.x >> 5) + warp;
     pdl_wait();
     if (r >= n_rows) return;
     const int src = row_index ? ld_act(row_index + r) : r;
@@ -114,13 +115,14 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, Ou
 extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* out, int out_dtype,
                             const int* row_index, int n_rows, int d, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (x_dtype == TUFF_F32 && n_rows >= 64 && d % 4 == 0 && d <= 128 * RMS_VEC && !((uintptr_t)x & 15) &&
+    if (x_dtype == TUFF_F32 && n_rows > 16 && d % 4 == 0 && d <= 128 * RMS_VEC && !((uintptr_t)x & 15) &&
         !((uintptr_t)w & 15) && !((uintptr_t)out & 15)) {
-        const dim3 grid(ceil_div(n_rows, 8));
+        const int warps = n_rows >= 2048 ? 8 : n_rows >= 512 ? 4 : n_rows >= 128 ? 2 : 1;
+        const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
         if (out_dtype == TUFF_BF16)
-            return launch_pdl(rmsnorm_rows_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)x, w, (bf16*)out, row_index, n_rows, d, eps);
+            return launch_pdl(rmsnorm_rows_kernel<bf16>, grid, block, 0, stream, (const float*)x, w, (bf16*)out, row_index, n_rows, d, eps);
         if (out_dtype == TUFF_F32)
-            return launch_pdl(rmsnorm_rows_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, w, (float*)out, row_index, n_rows, d, eps);
+            return launch_pdl(rmsnorm_rows_kernel<float>, grid, block, 0, stream, (const float*)x, w, (float*)out, row_index, n_rows, d, eps);
     }
     const int threads = 256;
     int rc = 0;

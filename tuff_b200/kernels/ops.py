@@ -159,7 +159,8 @@ def _tc_buffers(device: torch.device, need_bytes: int):
 
 def tc_status(device=None) -> int:
     """The status word of the tensor-core kernels (synchronises); non-zero means a bounded wait
-    ran out: 1 producer, 2 MMA issuer, 3 epilogue."""
+    ran out: in the tensor-core product 1 producer, 2 MMA issuer, 3 epilogue, 4 accumulator hand-back; in
+    attention 11/12 decode producer/consumer, 21/22 prefill producer/consumer."""
     out = 0
     for dev, st in _tc_state.items():
         if device is None or torch.device(device) == dev:
