@@ -240,6 +240,55 @@ def test_attention_finds_a_far_key_and_respects_the_window(dtype, hd, blocked):
             assert (out.float().cpu().numpy() - vals[far]).std() > 0.3
 
 
+@pytest.mark.parametrize("H,G,page,window", [(4, 2, 16, 0), (3, 1, 64, 0), (12, 2, 8, 100), (2, 2, 64, 129), (9, 3, 32, 0)])
+def test_attention_prefill_tc_long_portions(H, G, page, window):
+    """The tcgen05 kernel for prompt portions (head size 64): requests whose portions span several
+    128-token blocks and many 64-key tiles, start inside a page and inside a tile, with and without
+    a window, beside a single-token request; never-written cache slots hold NaN.  Against fp64."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(31)
+    hd = 64
+    starts, lens = (0, 70, 513, 5, 200), (300, 200, 129, 1, 128)
+    seqs = [a + n for a, n in zip(starts, lens)]
+    kp, vp, table = paged_setup(rng, seqs, G, hd, page, "bfloat16")
+    ks = [rng.normal(size=(n, G, hd)) for n in seqs]
+    vs = [rng.normal(size=(n, G, hd)) for n in seqs]
+    for r, n in enumerate(seqs):
+        ks[r][n // 3] *= 3.0                       # one key that stands out, so that a lost tile shows
+        for b in range(math.ceil(n / page)):
+            a, e = b * page, min(n, (b + 1) * page)
+            kp[table[r, b], :, :e - a] = dev(ks[r][a:e], torch.bfloat16).transpose(0, 1)
+            vp[table[r, b], :, :e - a] = dev(vs[r][a:e], torch.bfloat16).transpose(0, 1)
+    qs = [rng.normal(size=(n, H, hd)) for n in lens]
+    # q as a slice of a wider matrix, as the fused q/k/v product leaves it
+    wide = torch.zeros(sum(lens), (H + 2 * G) * hd, dtype=torch.bfloat16, device="cuda")
+    wide[:, :H * hd] = dev(np.concatenate(qs).reshape(-1, H * hd), torch.bfloat16)
+    q = wide[:, :H * hd]
+    pos = np.concatenate([np.arange(a, a + n) for a, n in zip(starts, lens)])
+    row_of = np.repeat(np.arange(len(lens)), lens)
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    assert ops.attention_prefill_tc_supported(q, kp, H, G, hd)
+    out = torch.full((sum(lens), H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.paged_attention(q, kp, vp, dev(table, torch.int32), dev(pos, torch.int32), dev(row_of, torch.int32), out, H, G, hd,
+                        1 / math.sqrt(hd), window=window, cu_q=dev(cu, torch.int32), all_single=False, max_seq_len=max(seqs))
+    ops.check_tc_status()
+    o = 0
+    for r, n in enumerate(lens):
+        qq = q[o:o + n].double().cpu().numpy().reshape(n, H, hd)
+        kk = dev(ks[r], torch.bfloat16).double().cpu().numpy()
+        vv = dev(vs[r], torch.bfloat16).double().cpu().numpy()
+        ref = np.zeros((n, H, hd))
+        kpos, qpos = np.arange(seqs[r])[None], (starts[r] + np.arange(n))[:, None]
+        hidden = (kpos > qpos) | ((kpos < qpos - window + 1) if window else False)
+        for h in range(H):
+            g = h // (H // G)
+            sc = np.where(hidden, -np.inf, qq[:, h] @ kk[:, g].T / math.sqrt(hd))
+            pr = np.exp(sc - sc.max(-1, keepdims=True))
+            ref[:, h] = (pr / pr.sum(-1, keepdims=True)) @ vv[:, g]
+        close(out[o:o + n], ref.reshape(n, H * hd), "bfloat16", scale=3.0)
+        o += n
+
+
 @pytest.mark.parametrize("V", [301, 65536, 5, 1025])
 def test_argmax_first_maximum(V):
     from tuff_b200.kernels import ops

@@ -8,6 +8,7 @@ raises (`tuff_b200.kernels.build.KernelBuildError`).
 from __future__ import annotations
 
 import ctypes
+import os
 import struct
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -445,6 +446,33 @@ def attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token,
            "attention_prefill")
 
 
+ATTN_TC_ENABLED = os.environ.get("TUFF_ATTN_TC", "1") != "0"
+
+
+def attention_prefill_tc_supported(q: torch.Tensor, k_pages: torch.Tensor, H: int, G: int, hd: int) -> bool:
+    """Whether the tcgen05 kernel for prompt portions takes these sizes and this query layout."""
+    if not ATTN_TC_ENABLED or q.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
+        return False
+    if q.data_ptr() % 16 or q.stride(0) % 8:
+        return False
+    lib = load_library("attention_tc")
+    return bool(lib.tuff_attention_prefill_tc_supported(c_int(H), c_int(G), c_int(hd), c_int(k_pages.shape[2])))
+
+
+def attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out, H, G, hd, scale,
+                         window: int = 0) -> None:
+    """Causal attention of prompt portions (bf16, head size 64) with tcgen05.mma: 128 query tokens
+    of one head per CTA, scores and weighted values accumulated in tensor memory."""
+    lib = load_library("attention_tc")
+    st = _tc_buffers(q.device, 0)
+    _check(lib.tuff_attention_prefill_tc(_ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
+                                         c_longlong(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]),
+                                         _ptr(positions), _ptr(cu_q), _ptr(out), _ptr(st["status"]),
+                                         c_int(q.shape[0]), c_int(cu_q.numel() - 1), c_int(H), c_int(G), c_int(hd),
+                                         c_int(k_pages.shape[2]), c_float(scale), c_int(window), _stream()),
+           "attention_prefill_tc")
+
+
 def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
                     window: int = 0, ctx=None, cu_q=None, all_single: bool | None = None,
                     max_seq_len: int | None = None) -> None:
@@ -456,6 +484,11 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, o
         all_single = ctx.all_single if all_single is None else all_single
         max_seq_len = ctx.max_seq_len if max_seq_len is None else max_seq_len
     assert q.stride(1) == 1 and out.shape == (q.shape[0], H * hd) and q.dtype == k_pages.dtype == out.dtype
+    if not all_single and cu_q is not None and attention_prefill_tc_supported(q, k_pages, H, G, hd):
+        _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
+        _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(cu_q, "cu_q")
+        attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out, H, G, hd, scale, window)
+        return
     if attention_flash_supported(q, k_pages, H, G, hd):
         _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
         _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")

@@ -118,7 +118,9 @@ def main(argv=None) -> int:
         else:
             pos = torch.arange(q_len, dtype=torch.int32, device=dev)
             cu = torch.tensor([0, q_len], dtype=torch.int32, device=dev)
-            fn = lambda: ops.attention_prefill(q, kp, vp, table, pos, row_of, cu, out, H, G, hd, hd ** -0.5, 0)
+            # the tcgen05 kernel where it applies (TUFF_ATTN_TC=0: the mma.sync one)
+            fn = lambda: ops.paged_attention(q, kp, vp, table, pos, row_of, out, H, G, hd, hd ** -0.5, 0, cu_q=cu,
+                                             all_single=False, max_seq_len=ctx_len)
             t = timed(fn, a.reps)
             flops = 2.0 * 2.0 * H * hd * q_len * (q_len + 1) / 2
             print(f"attention_prefill tokens={q_len} H={H} G={G} hd={hd} page={ps}: {t * 1e6:.1f} us, "
