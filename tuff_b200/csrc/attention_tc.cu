@@ -5,17 +5,24 @@
 // 64-key tiles its tokens can see.  Per tile:
 //     S  = Q K^T          tcgen05.mma, M=128 (query rows) x N=64 (keys) x K=head size, into TMEM
 //     P  = softmax part   four warps, one thread per query row (= one TMEM lane): tcgen05.ld of
-//                         the row's 64 scores, mask, running maximum and sum in fp32, exp2,
-//                         bf16 P written to shared memory in the 128-byte-swizzled K-major form
-//     PV = P V            tcgen05.mma, M=128 x N=head size x K=64 keys; V is used as it lies in
-//                         the cache page ([key][dim], dim contiguous), i.e. as an MN-major operand
-//     O  = O * corr + PV  in the row's registers (fp32), read back from TMEM
+//                         the row's 64 scores, mask, exp2 against the row's reference maximum,
+//                         bf16 P written back to tensor memory (tcgen05.st, two keys a column)
+//     O += P V            tcgen05.mma with the A operand (P) read from tensor memory, M=128 x
+//                         N=head size x K=64 keys, accumulated in TMEM over all tiles; V is used
+//                         as it lies in the cache page ([key][dim], dim contiguous), i.e. as an
+//                         MN-major shared-memory operand
+// P never passes through shared memory, whose bandwidth (Q, K and V are read from it by every
+// tile's MMAs, and TMA fills it) is the scarce resource of this kernel.
+// The exponentials of a row are taken against a reference maximum that is raised only when the
+// row's true maximum has grown by more than 2^8 beyond it (so no term exceeds 256); only then is
+// the accumulated O of that row rescaled, by a read-modify-write of its TMEM lane, and that is
+// rare after a row's first tiles.  Sum and output use the same reference, so the quotient is exact
+// whatever the reference was.
 // K and V tiles arrive through cp.async.bulk.tensor (one box per cache page, 128-byte swizzle)
-// in a ring of stages; a producer warp runs ahead.  S and PV are double-buffered in tensor memory
-// and P in shared memory, and the MMA thread issues S of tile j+1 before PV of tile j, so the
-// tensor cores work on the next scores while the softmax warps are busy with the current ones;
-// the softmax warps add PV of tile j only after they have handed over P of tile j+1.  Two CTAs
-// fit on an SM (256 of the 512 TMEM columns and about 100 KB of shared memory each).
+// in a ring of stages; a producer warp runs ahead.  S and P are double-buffered, and the MMA
+// thread issues S of tile j+1 before P V of tile j, so the tensor cores work on the next scores
+// while the softmax warps are busy with the current ones.  Two CTAs fit on an SM (256 of the 512
+// TMEM columns each: S twice 64, O 64, P twice 32).
 //
 // Online softmax as in the reference's kernel (src/lfm25_gpu.cu:506-558: scale 1/sqrt(hd) :520,
 // head-to-group map :518, causal bound :531), which handles one key at a time per block.
@@ -35,7 +42,7 @@
 namespace {
 constexpr int TILE = 64;                 // keys per tile
 constexpr int QROWS = 128;               // query tokens per CTA (UMMA M)
-constexpr int STAGES = 3;
+constexpr int STAGES = 4;
 constexpr int NUM_THREADS = 192;         // warps 0..3: softmax (TMEM lane quarter = warp), 4: TMA, 5: MMA + TMEM
 constexpr uint32_t MAX_POLLS = 1u << 26;
 
@@ -123,6 +130,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, 
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory: 128 lanes x 8 columns, two bf16 of K per column.
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -141,13 +154,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
 }
 
+// Writes 32 consecutive fp32 columns of this thread's TMEM lane; returns when they are in place.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n\t"
+                 "tcgen05.wait::st.sync.aligned;"
+                 :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+
 template <int HD> struct Smem {
     static constexpr int Q = 0;                               // [128][64] bf16
-    static constexpr int P = Q + QROWS * 128;                 // two tiles [128][64] bf16
-    static constexpr int KV = P + 2 * QROWS * 128;            // STAGES x (K tile, V tile)
+    static constexpr int KV = Q + QROWS * 128;                // STAGES x (K tile, V tile)
     static constexpr int STAGE_BYTES = 2 * TILE * HD * 2;
     static constexpr int BARS = KV + STAGES * STAGE_BYTES;
-    static constexpr int N_BARS = 1 + 2 * STAGES + 10;
+    static constexpr int N_BARS = 1 + 2 * STAGES + 8;
     static constexpr int TMEM_SLOT = BARS + N_BARS * 8;
     static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;       // + room to align the base to 1024 bytes
 };
@@ -175,7 +194,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
     auto s_empty = [&](int b) { return bars + 8u * (1 + 2 * STAGES + 2 + b); };
     auto p_full = [&](int b) { return bars + 8u * (1 + 2 * STAGES + 4 + b); };
     auto pv_full = [&](int b) { return bars + 8u * (1 + 2 * STAGES + 6 + b); };
-    auto pv_empty = [&](int b) { return bars + 8u * (1 + 2 * STAGES + 8 + b); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::TMEM_SLOT);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -205,11 +223,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
         for (int s = 0; s < STAGES; ++s) { mbar_init(kv_full(s), 1); mbar_init(kv_empty(s), 1); }
         for (int b = 0; b < 2; ++b) {
             mbar_init(s_full(b), 1); mbar_init(s_empty(b), 4); mbar_init(p_full(b), 4);
-            mbar_init(pv_full(b), 1); mbar_init(pv_empty(b), 4);
+            mbar_init(pv_full(b), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    constexpr uint32_t TMEM_COLS = 2 * TILE + 2 * HD;          // 256
+    constexpr uint32_t TMEM_COLS = 256;                        // S twice (128), O (64), P twice (32 each)
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(base + (uint32_t)L::TMEM_SLOT), "r"(TMEM_COLS) : "memory");
@@ -219,7 +237,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 2 * TILE;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * TILE, tmem_p = tmem_o + HD;
     bool ok = true;
 
     if (warp == 4) {
@@ -261,13 +279,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
                 if (j > 0) {
                     const int jj = j - 1, s = jj % STAGES, b = jj & 1;
                     if (!mbar_wait(p_full(b), (jj >> 1) & 1, p.status, 35)) { ok = false; break; }
-                    if (!mbar_wait(pv_empty(b), ((jj >> 1) & 1) ^ 1, p.status, 36)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sP = base + L::P + b * (QROWS * 128);
                     const uint32_t sV = base + L::KV + s * L::STAGE_BYTES + TILE * HD * 2;
 #pragma unroll
                     for (int k = 0; k < TILE / 16; ++k)
-                        umma(tmem_pv + b * HD, desc_k_major(sP + k * 32), desc_mn_major(sV + k * 2048), idesc_pv<HD>(), k > 0 ? 1u : 0u);
+                        umma_ts(tmem_o, tmem_p + b * (TILE / 2) + k * 8, desc_mn_major(sV + k * 2048), idesc_pv<HD>(), (jj > 0 || k > 0) ? 1u : 0u);
                     umma_commit(pv_full(b));
                     umma_commit(kv_empty(s));          // K and V of the stage have been read once these retire
                 }
@@ -297,105 +313,112 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(q_ready);
         }
-        float o[HD];
+        float m_ref = -INFINITY, l = 0.f;          // reference maximum (raw score units) and sum of exp2 against it
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int b = j & 1, s = j % STAGES;
+            const int key0 = (tile_lo + j) * TILE;
+            const bool live = warp_valid && key0 <= w_last && key0 + TILE - 1 >= warp_lo;
+            if (!mbar_wait(s_full(b), (j >> 1) & 1, p.status, 37)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sr[64];
+            if (live) tmem_ld64(tmem_s + lane_addr + b * TILE, sr);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty(b));
+            if (key0 + TILE - 1 > pos_last) {
+                // the last tile: value rows of keys that no token of this CTA sees may never have been written
+                if (!mbar_wait(kv_full(s), (j / STAGES) & 1, p.status, 38)) { ok = false; break; }
+                uint8_t* sV = base_ptr + L::KV + s * L::STAGE_BYTES + TILE * HD * 2;
+                const int first = pos_last + 1 - key0;                              // 1..63
+                for (int i = first * 8 + r; i < TILE * 8; i += QROWS)
+                    *reinterpret_cast<uint4*>(sV + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+                fence_async_smem();                                                 // before the MMA reads them
+            }
+            float mx = -INFINITY;
+            if (live) {
+                const bool need_mask = key0 + TILE - 1 > w_first || (p.window > 0 && key0 < w_first + 31 - p.window + 1) ||
+                                       warp * 32 + 31 >= n_here;
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains, not one of 64
+                if (need_mask) {                                                    // uniform over the warp
+                    const int c_lo = lo_r - key0, c_hi = hi_r - key0;               // visible columns of this row
 #pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;              // m in units of the raw score
-        float corr_prev = 0.f;                     // factor that O takes before P V of the tile before is added
-        bool live_prev = false;
-        for (int j = 0; j <= n_tiles && ok; ++j) {
+                    for (int c = 0; c < TILE; ++c) {
+                        const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sr[c]) : -INFINITY;
+                        sr[c] = __float_as_uint(v);
+                        mx4[c & 3] = fmaxf(mx4[c & 3], v);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < TILE; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+                }
+                mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            }
+            // raise the reference only when the maximum has outgrown it by more than 2^8
+            const bool raise = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > 8.f);
             float corr = 1.f;
-            bool live = false;
-            if (j < n_tiles) {
-                const int b = j & 1, s = j % STAGES;
-                const int key0 = (tile_lo + j) * TILE;
-                live = warp_valid && key0 <= w_last && key0 + TILE - 1 >= warp_lo;
-                if (!mbar_wait(s_full(b), (j >> 1) & 1, p.status, 37)) { ok = false; break; }
-                tc_fence_after();
-                uint32_t sr[64];
-                if (live) tmem_ld64(tmem_s + lane_addr + b * TILE, sr);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(s_empty(b));
-                if (key0 + TILE - 1 > pos_last) {
-                    // the last tile: value rows of keys that no token of this CTA sees may never have been written
-                    if (!mbar_wait(kv_full(s), (j / STAGES) & 1, p.status, 38)) { ok = false; break; }
-                    uint8_t* sV = base_ptr + L::KV + s * L::STAGE_BYTES + TILE * HD * 2;
-                    const int first = pos_last + 1 - key0;                          // 1..63
-                    for (int i = first * 8 + r; i < TILE * 8; i += QROWS)
-                        *reinterpret_cast<uint4*>(sV + i * 16) = make_uint4(0u, 0u, 0u, 0u);
-                }
-                if (live) {
-                    const bool need_mask = key0 + TILE - 1 > w_first || (p.window > 0 && key0 < w_first + 31 - p.window + 1) ||
-                                           warp * 32 + 31 >= n_here;
-                    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 64
-                    if (need_mask) {                                                // uniform over the warp
-                        const int c_lo = lo_r - key0, c_hi = hi_r - key0;           // visible columns of this row
-#pragma unroll
-                        for (int c = 0; c < TILE; ++c) {
-                            const float v = (c >= c_lo && c <= c_hi) ? __uint_as_float(sr[c]) : -INFINITY;
-                            sr[c] = __float_as_uint(v);
-                            mx4[c & 3] = fmaxf(mx4[c & 3], v);
-                        }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < TILE; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
-                    }
-                    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                    const float m_new = fmaxf(m, mx);
-                    const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-                    corr = ex2((m - m_safe) * p.scale_log2);                        // exp2(-inf) = 0
-                    const float nb = -m_safe * p.scale_log2;
-                    m = m_new;
-                    float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-                    uint8_t* prow = base_ptr + L::P + b * (QROWS * 128) + r * 128;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {                                   // 16-byte chunk c of the row, swizzled
-                        float e[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            e[i] = ex2(fmaf(__uint_as_float(sr[8 * c + i]), p.scale_log2, nb));
-                            sum4[i & 3] += e[i];
-                        }
-                        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
-                            make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
-                    }
-                    l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_full(b));
+            if (raise) {
+                corr = m_ref == -INFINITY ? 0.f : ex2((m_ref - mx) * p.scale_log2);
+                l *= corr;
+                m_ref = mx;
             }
-            if (j > 0) {
-                const int jj = j - 1, b = jj & 1;
-                if (!mbar_wait(pv_full(b), (jj >> 1) & 1, p.status, 39)) { ok = false; break; }
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {
+                // O holds the tiles before this one: wait for the last of them, then rescale this lane
+                if (!mbar_wait(pv_full((j - 1) & 1), ((j - 1) >> 1) & 1, p.status, 39)) { ok = false; break; }
                 tc_fence_after();
-                if (live_prev) {
 #pragma unroll
-                    for (int d0 = 0; d0 < HD; d0 += 32) {
-                        uint32_t pr[32];
-                        tmem_ld32(tmem_pv + lane_addr + b * HD + d0, pr);
+                for (int d0 = 0; d0 < HD; d0 += 32) {
+                    uint32_t orow[32];
+                    tmem_ld32(tmem_o + lane_addr + d0, orow);
 #pragma unroll
-                        for (int d = 0; d < 32; ++d) o[d0 + d] = fmaf(o[d0 + d], corr_prev, __uint_as_float(pr[d]));
-                    }
+                    for (int d = 0; d < 32; ++d) orow[d] = __float_as_uint(__uint_as_float(orow[d]) * corr);
+                    tmem_st32(tmem_o + lane_addr + d0, orow);
                 }
                 tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(pv_empty(b));
             }
-            corr_prev = corr; live_prev = live;
+            // P of two tiles ago has been read once its P V has retired
+            if (j >= 2 && !mbar_wait(pv_full(b), ((j - 2) >> 1) & 1, p.status, 40)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t w[32];                                                         // the row's P, two keys a word
+            if (live) {
+                const float nb = m_ref == -INFINITY ? 0.f : -m_ref * p.scale_log2;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < TILE; c += 2) {
+                    const float e0 = ex2(fmaf(__uint_as_float(sr[c]), p.scale_log2, nb));
+                    const float e1 = ex2(fmaf(__uint_as_float(sr[c + 1]), p.scale_log2, nb));
+                    sum4[(c >> 1) & 3] += e0 + e1;
+                    w[c >> 1] = pack_bf16(e0, e1);
+                }
+                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) w[c] = 0u;
+            }
+            tmem_st32(tmem_p + lane_addr + b * (TILE / 2), w);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(b));
         }
-        if (ok && valid) {
+        if (ok && !mbar_wait(pv_full((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, p.status, 41)) ok = false;
+        tc_fence_after();
+        if (ok && warp_valid) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* orow = p.out + ((size_t)(q0 + r) * p.H + h) * HD;
 #pragma unroll
-            for (int c = 0; c < HD / 8; ++c) {
-                uint4 v;
-                v.x = pack_bf16(o[8 * c] * inv, o[8 * c + 1] * inv);
-                v.y = pack_bf16(o[8 * c + 2] * inv, o[8 * c + 3] * inv);
-                v.z = pack_bf16(o[8 * c + 4] * inv, o[8 * c + 5] * inv);
-                v.w = pack_bf16(o[8 * c + 6] * inv, o[8 * c + 7] * inv);
-                *reinterpret_cast<uint4*>(orow + 8 * c) = v;
+            for (int d0 = 0; d0 < HD; d0 += 32) {
+                uint32_t o[32];
+                tmem_ld32(tmem_o + lane_addr + d0, o);
+                if (valid) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 v;
+                        v.x = pack_bf16(__uint_as_float(o[8 * c]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
+                        v.y = pack_bf16(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
+                        v.z = pack_bf16(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
+                        v.w = pack_bf16(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + d0 + 8 * c) = v;
+                    }
+                }
             }
         }
     }
