@@ -101,7 +101,8 @@ def test_swiglu(dtype, F, n):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("d,K,lens", [(80, 3, (5, 1, 2, 9)), (96, 4, (1, 1, 1)), (200, 2, (7, 2)), (64, 5, (3, 2, 1, 11))])
+@pytest.mark.parametrize("d,K,lens", [(80, 3, (5, 1, 2, 9)), (96, 4, (1, 1, 1)), (200, 2, (7, 2)), (64, 5, (3, 2, 1, 11)),
+                                      (80, 3, (40, 1, 13, 50, 2)), (96, 4, (33, 2, 31)), (200, 2, (70, 9)), (64, 5, (30, 41))])
 def test_shortconv_continues_state(dtype, d, K, lens):
     """Portions of any length (also shorter than K-1) continue each row's state; slots are not
     in row order; the rolled state equals the last K-1 values of u."""

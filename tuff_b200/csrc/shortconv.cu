@@ -96,6 +96,90 @@ __global__ void shortconv_fwd_vec_kernel(const bf16* __restrict__ bcx, const flo
     *reinterpret_cast<uint4*>(out + (size_t)t * d + c) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// bf16, d % 8 == 0, K known at compile time: a thread takes 8 neighbouring channels of RUN
+// consecutive tokens, keeps the last K-1 values of u in registers while it walks them, and so
+// reads B, C and x of every token once (the kernel above reads B and x K times).  The history is
+// rebuilt where a run starts and where a new request's portion starts inside it.  The taps are
+// applied in the same ascending order, so the result is the same to the bit.
+template <int K, int RUN>
+__global__ void __launch_bounds__(128)
+shortconv_fwd_run_kernel(const bf16* __restrict__ bcx, const float* __restrict__ taps,
+                         const float* __restrict__ state, const int* __restrict__ slot_of_row,
+                         const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
+                         bf16* __restrict__ out, int n_tokens, int d) {
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    const int t0 = blockIdx.x * RUN;
+    if (c >= d) return;
+    const size_t ld = (size_t)3 * d;
+    float tap[K][8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+        for (int j = 0; j < K; ++j) tap[j][e] = taps[(size_t)(c + e) * K + j];
+    float hist[K - 1][8];                              // u of the K-1 tokens before the current one, oldest first
+    const int t1 = min(n_tokens, t0 + RUN);
+    // the loads of the run's tokens are independent of one another: issue them four tokens at a time
+    for (int tb = t0; tb < t1; tb += 4) {
+        uint4 vb[4], vc[4], vx[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (tb + q < t1) {
+                const bf16* p = bcx + (size_t)(tb + q) * ld + c;
+                vb[q] = *reinterpret_cast<const uint4*>(p);
+                vc[q] = *reinterpret_cast<const uint4*>(p + d);
+                vx[q] = *reinterpret_cast<const uint4*>(p + 2 * d);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int t = tb + q;
+            if (t >= t1) break;
+            const int r = row_of_token[t];
+            const int i = t - cu_q[r];
+            if (t == t0 || i == 0) {
+                const float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) {
+                    const int back = (K - 1) - j;
+                    if (i - back >= 0) {
+                        const bf16* p = bcx + (size_t)(t - back) * ld + c;
+                        float b[8], x[8];
+                        unpack8(*reinterpret_cast<const uint4*>(p), b);
+                        unpack8(*reinterpret_cast<const uint4*>(p + 2 * d), x);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) hist[j][e] = b[e] * x[e];
+                    } else {
+                        const float* sp = st + (size_t)((K - 1) + (i - back)) * d + c;
+                        const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+                        hist[j][0] = s0.x; hist[j][1] = s0.y; hist[j][2] = s0.z; hist[j][3] = s0.w;
+                        hist[j][4] = s1.x; hist[j][5] = s1.y; hist[j][6] = s1.z; hist[j][7] = s1.w;
+                    }
+                }
+            }
+            float b[8], g[8], x[8], y[8];
+            unpack8(vb[q], b); unpack8(vc[q], g); unpack8(vx[q], x);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float u = b[e] * x[e];
+                float acc = 0.f;
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) acc = fmaf(tap[j][e], hist[j][e], acc);
+                y[e] = fmaf(tap[K - 1][e], u, acc);
+#pragma unroll
+                for (int j = 0; j + 1 < K - 1; ++j) hist[j][e] = hist[j + 1][e];
+                hist[K - 2][e] = u;
+            }
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(g[2 * e] * y[2 * e], g[2 * e + 1] * y[2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            *reinterpret_cast<uint4*>(out + (size_t)t * d + c) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+}
+
 // New state entry s (0 = oldest) is u at portion index n-(K-1)+s; if that is
 // negative it is the old entry s+n.  Ascending s reads old entries before they
 // are overwritten, since s+n > s.
@@ -170,7 +254,19 @@ extern "C" int tuff_shortconv(const void* bcx, void* out, int dtype, const float
                                                                  row_of_token, cu_q, (float*)out, n_tokens, d, K);
         shortconv_state_kernel<float><<<g2, threads, 0, stream>>>((const float*)bcx, state, slot_of_row, cu_q, d, K);
     } else if (dtype == TUFF_BF16) {
-        if (d % 8 == 0 && !((uintptr_t)bcx & 15) && !((uintptr_t)out & 15) && !((uintptr_t)state & 15))
+        const bool vec = d % 8 == 0 && !((uintptr_t)bcx & 15) && !((uintptr_t)out & 15) && !((uintptr_t)state & 15);
+        constexpr int RUN = 8;
+        const dim3 gr(ceil_div(n_tokens, RUN), ceil_div(d / 8, threads));
+        if (vec && n_tokens >= 4 * RUN && K == 3)
+            shortconv_fwd_run_kernel<3, RUN><<<gr, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row, row_of_token,
+                                                                          cu_q, (bf16*)out, n_tokens, d);
+        else if (vec && n_tokens >= 4 * RUN && K == 2)
+            shortconv_fwd_run_kernel<2, RUN><<<gr, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row, row_of_token,
+                                                                          cu_q, (bf16*)out, n_tokens, d);
+        else if (vec && n_tokens >= 4 * RUN && K == 4)
+            shortconv_fwd_run_kernel<4, RUN><<<gr, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row, row_of_token,
+                                                                          cu_q, (bf16*)out, n_tokens, d);
+        else if (vec)
             shortconv_fwd_vec_kernel<<<dim3(n_tokens, ceil_div(d / 8, threads)), threads, 0, stream>>>(
                 (const bf16*)bcx, taps, state, slot_of_row, row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
         else
