@@ -55,7 +55,8 @@ def test_rmsnorm(dtype, d, n, eps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("M,N,K", [(1, 301, 80), (7, 130, 200), (65, 64, 48), (130, 257, 1000), (3, 2048, 5632)])
+@pytest.mark.parametrize("M,N,K", [(1, 301, 80), (7, 130, 200), (65, 64, 48), (130, 257, 1000), (3, 2048, 5632),
+                                   (300, 520, 136), (512, 2048, 192), (257, 129, 72), (1100, 777, 2048)])
 def test_linear(dtype, M, N, K):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(2)
@@ -72,6 +73,35 @@ def test_linear(dtype, M, N, K):
     logits = torch.empty(M, N, dtype=torch.float32, device="cuda")
     ops.linear(a, w, logits)
     close(logits, ref, "float32", scale=4.0 if dtype == "float32" else 1.0)   # fp32 out even from bf16 operands
+
+
+def test_linear_by_cta_pairs():
+    """The tensor-core product computed by pairs of CTAs (an option, off by default): ragged sizes
+    against fp64, in a process of its own since the switch is read once."""
+    import subprocess, sys, os
+    code = """
+import numpy as np, torch
+from tuff_b200.kernels import ops
+rng = np.random.default_rng(41)
+for M, N, K in ((300, 520, 136), (512, 2048, 192), (257, 129, 72), (1100, 777, 2048)):
+    a = torch.tensor(rng.normal(size=(M, K)), dtype=torch.bfloat16, device='cuda')
+    w = torch.tensor(rng.normal(size=(N, K)) * 0.05, dtype=torch.bfloat16, device='cuda')
+    ref = a.double().cpu().numpy() @ w.double().cpu().numpy().T
+    out = torch.empty(M, N, dtype=torch.bfloat16, device='cuda')
+    ops.gemm_tc(a, w, out)
+    acc = torch.ones(M, N, device='cuda')
+    ops.gemm_tc(a, w, acc, accumulate=True)
+    ops.check_tc_status()
+    tol = 2e-2 * max(1.0, np.abs(ref).max())
+    assert np.abs(out.double().cpu().numpy() - ref).max() <= 2 * tol, (M, N, K)
+    assert np.abs(acc.double().cpu().numpy() - 1 - ref).max() <= 1e-3 * max(1.0, np.abs(ref).max()), (M, N, K)
+print('pairs ok')
+"""
+    env = dict(os.environ, TUFF_GEMM_PAIR="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "pairs ok" in r.stdout, r.stdout + r.stderr
 
 
 def test_linear_is_batch_invariant():
