@@ -736,7 +736,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         p.a_rows = N; p.b_rows = M;
         const int tiles = ceil_div(N, BM);
         if (tiles < 148 && k_blocks > 1) {
-            splits = ceil_div(296, tiles);
+            splits = 148 / tiles > 0 ? 148 / tiles : 1;     // one wave of work items: fewer, larger items
             if (splits > 16) splits = 16;
             if (splits > k_blocks) splits = k_blocks;
             const long long need = (long long)splits * M * N * 4;
