@@ -155,6 +155,8 @@ def register_toy_parts():
 
     @register_mixer("toy_ema")
     class ToyEma(Mixer):
+        replayable = False                  # walks the rows on the host
+
         def __init__(self, d_model):
             self.d = d_model
 
@@ -263,6 +265,172 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     rc = runner.open("again")
     logits = f64(runner.step([StepEntry(rc, seqs["a"], [len(seqs["a"]) - 1])]))
     np.testing.assert_allclose(logits[0], refs["a"][-1], atol=2e-4, rtol=2e-4)
+
+
+def register_toy_routed_ffn_and_position_encoding():
+    """A feed-forward with routing (each token goes to the one of E small experts whose router
+    logit is largest, its output scaled by the softmax weight of that logit) and a position
+    encoding with pairing of neighbours (element 2j with 2j+1) and its own angle law, both defined
+    here and nowhere in the package."""
+    from tuff_b200.kernels import ops
+    from tuff_b200.parts import (FEED_FORWARDS, FeedForward, PositionEncoding, WeightDecl, register_feed_forward,
+                                 register_position_encoding)
+    if "toy_top1_experts" in FEED_FORWARDS.kinds():
+        return
+
+    @register_feed_forward("toy_top1_experts")
+    class ToyTop1(FeedForward):
+        replayable = False                  # the rows of an expert are gathered on the host's say
+
+        def __init__(self, d_model, ffn_dim, n_experts):
+            self.d, self.F, self.E = d_model, ffn_dim, n_experts
+
+        def weight_decls(self):
+            decls = {"router": WeightDecl((self.E, self.d))}
+            for e in range(self.E):
+                decls[f"up{e}"] = WeightDecl((self.F, self.d))
+                decls[f"down{e}"] = WeightDecl((self.d, self.F))
+            return decls
+
+        def forward(self, ctx, h, residual):
+            T = h.shape[0]
+            logits = torch.empty((T, self.E), dtype=torch.float32, device=h.device)
+            ops.linear(h, self.w["router"], logits)                 # router logits in fp32
+            weight, expert = torch.softmax(logits, -1).max(-1)
+            for e in range(self.E):
+                idx = torch.nonzero(expert == e).flatten()
+                if idx.numel() == 0:
+                    continue
+                he = h[idx].contiguous()
+                mid = torch.empty((idx.numel(), self.F), dtype=h.dtype, device=h.device)
+                ops.linear(he, self.w[f"up{e}"], mid)
+                mid = torch.relu(mid)
+                out = torch.zeros((idx.numel(), self.d), dtype=torch.float32, device=h.device)
+                ops.linear(mid, self.w[f"down{e}"], out, accumulate=True)
+                residual[idx] += out * weight[idx, None]
+
+    @register_position_encoding("toy_pairs")
+    class ToyPairs(PositionEncoding):
+        """Rotates (x[2j], x[2j+1]) by pos / (j + 1): no table for the fused kernel, so the
+        attention mixer calls `rotate` between its norm and its cache write."""
+
+        def __init__(self, head_dim):
+            self.hd = head_dim
+
+        def rotate(self, ctx, q, k):
+            j = torch.arange(self.hd // 2, device=q.device, dtype=torch.float32)
+            ang = ctx.positions.float()[:, None] / (j + 1)[None]
+            c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            for x in (q, k):
+                if x is None:
+                    continue
+                x0, x1 = x[..., 0::2].float().clone(), x[..., 1::2].float().clone()
+                x[..., 0::2] = (x0 * c - x1 * s_).to(x.dtype)
+                x[..., 1::2] = (x0 * s_ + x1 * c).to(x.dtype)
+
+
+def test_toy_routed_feed_forward_and_position_encoding(tmp_path):
+    """Layers that differ in feed-forward and position encoding within one model: layer 0 has the
+    toy position encoding and the toy routed feed-forward, layer 1 the package's rotary encoding and
+    SwiGLU.  Stepped in portions and compared with a plain forward over the whole sequence."""
+    from tuff_b200.config import Architecture, register_architecture
+    from tuff_b200.engine import ModelRunner
+    from tuff_b200.models import LayerSpec, ModelSpec
+    from tuff_b200.parts import PartSpec
+    from tuff_b200.weights import write_random_model
+    register_toy_routed_ffn_and_position_encoding()
+    d, V, F, E, H, G, hd = 40, 61, 24, 3, 4, 2, 8
+
+    def spec(cfg):
+        layers = []
+        for i in range(2):
+            p = f"l{i}."
+            pe = PartSpec("toy_pairs", dict(head_dim=hd)) if i == 0 else PartSpec("rope_neox", dict(head_dim=hd, theta=500.0))
+            mixer = PartSpec("gqa_attention", dict(d_model=d, num_heads=H, num_kv_heads=G, head_dim=hd, qk_norm_eps=None,
+                                                   position_encoding=pe),
+                             {n: p + n for n in ("q_proj", "k_proj", "v_proj", "out_proj")})
+            if i == 0:
+                names = {"router": p + "router"}
+                for e in range(E):
+                    names[f"up{e}"], names[f"down{e}"] = p + f"up{e}", p + f"down{e}"
+                ffn = PartSpec("toy_top1_experts", dict(d_model=d, ffn_dim=F, n_experts=E), names)
+            else:
+                ffn = PartSpec("swiglu", dict(d_model=d, ffn_dim=F), {n: p + n for n in ("w1", "w2", "w3")})
+            layers.append(LayerSpec(mixer=mixer, ffn=ffn,
+                                    mixer_norm=PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": p + "n1"}),
+                                    ffn_norm=PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": p + "n2"})))
+        return ModelSpec("ToyRoutedLM", d, V, PartSpec("token_embedding", dict(vocab_size=V, d_model=d), {"weight": "emb"}),
+                         layers, PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": "nf"}),
+                         PartSpec("lm_head", dict(vocab_size=V, d_model=d), {"weight": "emb"}))
+
+    register_architecture(Architecture("ToyRoutedLM", lambda raw, where: raw, spec, lambda c: dict(c)))
+    folder = write_random_model(str(tmp_path / "routed"), dict(architectures=["ToyRoutedLM"]), 9, store_dtype=torch.float32)
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    # the router's rows far apart, so that the choice of expert does not hang on rounding
+    w = {k: np.asarray(v, np.float64) for k, v in w.items()}
+
+    def attention(h, p, toy):
+        T = h.shape[0]
+        q = (h @ w[p + "q_proj"].T).reshape(T, H, hd)
+        k = (h @ w[p + "k_proj"].T).reshape(T, G, hd)
+        v = (h @ w[p + "v_proj"].T).reshape(T, G, hd)
+        pos = np.arange(T)
+        if toy:
+            ang = pos[:, None] / (np.arange(hd // 2) + 1)[None]
+            c, s_ = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+            def rot(x):
+                y = x.copy()
+                y[..., 0::2] = x[..., 0::2] * c - x[..., 1::2] * s_
+                y[..., 1::2] = x[..., 0::2] * s_ + x[..., 1::2] * c
+                return y
+            q, k = rot(q), rot(k)
+        else:
+            q, k = plain.rope_neox(q, pos, 500.0), plain.rope_neox(k, pos, 500.0)
+        out = np.zeros((T, H, hd))
+        for hh in range(H):
+            g = hh // (H // G)
+            sc = np.where(pos[None] > pos[:, None], -np.inf, q[:, hh] @ k[:, g].T / np.sqrt(hd))
+            pr = np.exp(sc - sc.max(-1, keepdims=True))
+            out[:, hh] = (pr / pr.sum(-1, keepdims=True)) @ v[:, g]
+        return out.reshape(T, H * hd) @ w[p + "out_proj"].T
+
+    def forward(tokens):
+        x = w["emb"][tokens]
+        margins = []
+        for i in range(2):
+            p = f"l{i}."
+            x = x + attention(plain.rms_norm(x, w[p + "n1"], 1e-5), p, i == 0)
+            h = plain.rms_norm(x, w[p + "n2"], 1e-5)
+            if i == 0:
+                lg = h @ w[p + "router"].T
+                pr = np.exp(lg - lg.max(-1, keepdims=True)); pr /= pr.sum(-1, keepdims=True)
+                srt = np.sort(lg, -1)
+                margins.append(srt[:, -1] - srt[:, -2])
+                o = np.zeros_like(x)
+                for t in range(len(tokens)):
+                    e = int(lg[t].argmax())
+                    o[t] = (np.maximum(h[t] @ w[p + f"up{e}"].T, 0) @ w[p + f"down{e}"].T) * pr[t, e]
+                x = x + o
+            else:
+                x = x + plain.swiglu_ffn(h, w[p + "w1"], w[p + "w3"], w[p + "w2"])
+        return plain.lm_head(x, w["nf"], 1e-5, w["emb"]), np.concatenate(margins)
+
+    rng = np.random.default_rng(12)
+    tokens = rng.integers(0, V, 37).tolist()
+    ref, margin = forward(tokens)
+    decided = margin > 1e-4                        # tokens whose expert does not hang on rounding
+    assert decided.mean() > 0.9
+    runner = ModelRunner(folder, dtype="float32", max_tokens=64, page_size=4, max_requests=2)
+    assert not runner.cuda_graphs                  # a part said it cannot be replayed
+    rc = runner.open("r")
+    pos = 0
+    for n in (5, 1, 1, 1, 2, 12, 1, 8, 6):
+        logits = f64(runner.step([StepEntry(rc, tokens[pos:pos + n], list(range(n)))]))
+        # a token routed differently would change every later position of the sequence
+        if decided[:pos + n].all():
+            np.testing.assert_allclose(logits, ref[pos:pos + n], atol=3e-4, rtol=3e-4)
+        pos += n
+    assert decided.all() or pos == len(tokens)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

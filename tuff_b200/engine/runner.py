@@ -62,7 +62,7 @@ class ModelRunner:
                 weights = random_device_tensors(self.model.expected_tensors(), weight_seed, self.dtype, self.device)
             self.model.bind_weights(weights, self.dtype)
         del weights
-        self.cuda_graphs = bool(cuda_graphs)
+        self.cuda_graphs = bool(cuda_graphs) and self.model.replayable     # every part must allow replay
         self._graphs: Dict[int, dict] = {}
         self._seen_rows: Dict[int, int] = {}
         self.graph_replays = 0

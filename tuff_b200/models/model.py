@@ -37,6 +37,9 @@ class Model:
                             (bl.mixer_norm, ls.mixer_norm), (bl.ffn_norm, ls.ffn_norm)]
         self.schedule: List[ScheduleEntry] = spec.resolved_schedule()
         self.act_dtype: torch.dtype | None = None
+        # a position encoding is built inside its mixer; it counts too
+        self.replayable = all(getattr(part, "replayable", True) and
+                              getattr(getattr(part, "pos", None), "replayable", True) for part, _ in self._bound)
 
     # ---- weights -----------------------------------------------------------
     def expected_tensors(self) -> Dict[str, WeightDecl]:

@@ -71,6 +71,13 @@ class PartSpec:
 
 class Part:
     kind: str = ""
+    # Whether a step that runs this part can be captured once and replayed as a CUDA graph: its
+    # forward then launches the same kernels on the same buffers whatever the step's values are,
+    # reads nothing on the host (no `ctx.host`, no `.item()`, no shape that depends on data) and
+    # takes everything that changes from step to step from the context's device tensors.  A part
+    # that cannot promise this sets it to False, and a model with such a part runs every step as
+    # plain launches.
+    replayable: bool = True
 
     def weight_decls(self) -> Dict[str, WeightDecl]:
         return {}
