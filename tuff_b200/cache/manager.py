@@ -67,6 +67,16 @@ class RequestCache:
     slot: int = -1
     reserved: int = 0                                   # tokens reserved beyond n_tokens for the running step
     open: bool = True
+    stamp: int = 0                                      # bumped whenever a table changes
+    _arrays: Dict[int, tuple] = field(default_factory=dict)   # group -> (stamp, table as int32 array)
+
+    def table_array(self, group: int) -> np.ndarray:
+        """The group's table as an int32 array, rebuilt only after the table changed (a decoding
+        request takes a page once in page_size steps, and its table may hold hundreds)."""
+        hit = self._arrays.get(group)
+        if hit is None or hit[0] != self.stamp:
+            hit = self._arrays[group] = (self.stamp, np.asarray(self.tables[group], dtype=np.int32))
+        return hit[1]
 
 
 class CacheManager:
@@ -142,7 +152,9 @@ class CacheManager:
                 raise OutOfPages(f"request {rc.request_id!r} needs {n} more page(s) for {n_new} token(s); "
                                  f"{g.pool.n_free} of {g.pool.n_units} free")
         for g, n, table in zip(self.groups, need, rc.tables):
-            table.extend(g.pool.take(n))
+            if n:
+                table.extend(g.pool.take(n))
+                rc.stamp += 1
         rc.reserved += n_new
 
     def cancel(self, rc: RequestCache) -> None:
@@ -151,6 +163,7 @@ class CacheManager:
         for g, table in zip(self.groups, rc.tables):
             while len(table) > blocks:
                 g.pool.give_back(table.pop())
+                rc.stamp += 1
         rc.reserved = 0
 
     def commit(self, rc: RequestCache, n_new: int) -> None:
@@ -170,6 +183,7 @@ class CacheManager:
                 if table[b] != NO_PAGE:
                     g.pool.give_back(table[b])
                     table[b] = NO_PAGE
+                    rc.stamp += 1
                 b += 1
 
     def close(self, rc: RequestCache) -> None:
@@ -180,6 +194,7 @@ class CacheManager:
                 if p != NO_PAGE:
                     g.pool.give_back(p)
             table.clear()
+        rc.stamp += 1
         self.slots.give_back(rc.slot)
         rc.open = False
         rc.slot = -1
@@ -191,8 +206,8 @@ class CacheManager:
         w = max([len(rc.tables[group]) for rc in rcs] + [1]) if width is None else width
         out = np.full((len(rcs), w), NO_PAGE, dtype=np.int32)
         for i, rc in enumerate(rcs):
-            t = rc.tables[group]
-            out[i, :len(t)] = t
+            t = rc.table_array(group)
+            out[i, :t.size] = t
         return out
 
     def free_tokens(self) -> int:

@@ -542,7 +542,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int m0 = (w % mt) * 2 * BM + (int)rank * BM, n0 = (w / mt) * BN + (int)rank * (BN / 2);
                 for (int i = 0; i < p.k_blocks; ++i, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, p.status, 11)) { ok = false; break; }
+                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, p.status, 51)) { ok = false; break; }
                     // the first CTA's barrier counts the bytes of both CTAs
                     if (rank == 0) mbar_expect_tx(full_bar(s), 2 * (L::A_BYTES + L::B_BYTES));
                     const uint32_t fb = mapa(full_bar(s), 0);
@@ -558,12 +558,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t it = 0, tile = 0;
             for (int w = pair; w < n_work && ok; w += n_pairs, ++tile) {
                 const uint32_t buf = tile & 1u;
-                if (!mbar_wait(acc_empty(buf), ((tile >> 1) & 1u) ^ 1u, p.status, 14)) { ok = false; break; }
+                if (!mbar_wait(acc_empty(buf), ((tile >> 1) & 1u) ^ 1u, p.status, 54)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + buf * BN;
                 for (int i = 0; i < p.k_blocks; ++i, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, p.status, 12)) { ok = false; break; }
+                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, p.status, 52)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a = a_tiles + s * L::A_BYTES, b = b_tiles + s * L::B_BYTES;
 #pragma unroll
@@ -581,7 +581,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int w = pair; w < n_work && ok; w += n_pairs, ++tile) {
             const int m0 = (w % mt) * 2 * BM + (int)rank * BM, n0 = (w / mt) * BN;
             const uint32_t buf = tile & 1u;
-            if (!mbar_wait(acc_full(buf), (tile >> 1) & 1u, p.status, 13)) { ok = false; break; }
+            if (!mbar_wait(acc_full(buf), (tile >> 1) & 1u, p.status, 53)) { ok = false; break; }
             tc_fence_after();
             write_tile<BN>(p, base_ptr + L::OUT_STAGE + (warp - 2) * 2048, tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN,
                            m0, n0, 0, quad, lane);

@@ -69,9 +69,14 @@ def validate_entries(entries: Sequence[StepEntry], vocab_size: int, max_context:
         n = len(e.tokens)
         if n < 1:
             raise BatchError(f"request {rid!r}: an entry needs at least one token")
-        for t in e.tokens:
-            if not 0 <= int(t) < vocab_size:
-                raise BatchError(f"request {rid!r}: token {t} is outside the vocabulary (0..{vocab_size - 1})")
+        if n == 1:
+            bad = not 0 <= int(e.tokens[0]) < vocab_size
+        else:
+            a = np.asarray(e.tokens, dtype=np.int64)
+            bad = int(a.min()) < 0 or int(a.max()) >= vocab_size
+        if bad:
+            t = next(t for t in e.tokens if not 0 <= int(t) < vocab_size)
+            raise BatchError(f"request {rid!r}: token {t} is outside the vocabulary (0..{vocab_size - 1})")
         for w in e.want:
             if not 0 <= int(w) < n:
                 raise BatchError(f"request {rid!r}: wanted place {w} is outside its {n} token(s)")

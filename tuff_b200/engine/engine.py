@@ -73,7 +73,8 @@ class Engine:
             if e.samples:
                 r = e.request
                 p = r.params
-                recent = r.all_tokens()[-p.repeat_last_n:] if (p.repeat_penalty > 1.0 and p.repeat_last_n) else ()
+                n_all = len(r.prompt) + len(r.output)
+                recent = r.token_slice(n_all - p.repeat_last_n) if (p.repeat_penalty > 1.0 and p.repeat_last_n) else ()
                 rows.append(SampleRow(p, r.key, len(r.output), recent))
         out: List[int] = []
         if rows:

@@ -65,6 +65,19 @@ class Request:
     def all_tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def token_slice(self, start: int, stop: int | None = None) -> List[int]:
+        """Tokens start..stop-1 of prompt followed by output, without building the whole list
+        (a decode step asks for one token of a request that may hold thousands)."""
+        n_p = len(self.prompt)
+        total = n_p + len(self.output)
+        stop = total if stop is None else min(stop, total)
+        start = max(0, start)
+        if start >= n_p:
+            return self.output[start - n_p:stop - n_p]
+        if stop <= n_p:
+            return self.prompt[start:stop]
+        return self.prompt[start:] + self.output[:stop - n_p]
+
     def n_pending(self) -> int:
         return len(self.prompt) + len(self.output) - self.n_cached
 
@@ -197,7 +210,7 @@ class Scheduler:
             if req.status is not RequestStatus.RUNNING or not self._fits(need, free):
                 continue
             self._take(need, free)
-            plan.entries.append(PlannedEntry(req, req.all_tokens()[req.n_cached:], True))
+            plan.entries.append(PlannedEntry(req, req.token_slice(req.n_cached), True))
             planned.add(id(req))
             budget -= 1
         # 2. portions of running prompts
@@ -208,7 +221,7 @@ class Scheduler:
             if n < 1:
                 continue
             self._take(self.cache.pages_needed(req.cache, n), free)
-            toks = req.all_tokens()[req.n_cached:req.n_cached + n]
+            toks = req.token_slice(req.n_cached, req.n_cached + n)
             plan.entries.append(PlannedEntry(req, toks, n == req.n_pending()))
             planned.add(id(req))
             budget -= n
@@ -225,7 +238,7 @@ class Scheduler:
             plan.admitted.append(req)
             self.stats["admitted"] += 1
             self._take(self.cache.pages_needed(req.cache, n), free)
-            plan.entries.append(PlannedEntry(req, req.all_tokens()[:n], n == req.n_pending()))
+            plan.entries.append(PlannedEntry(req, req.token_slice(0, n), n == req.n_pending()))
             planned.add(id(req))
             budget -= n
 

@@ -160,8 +160,11 @@ def _tc_buffers(device: torch.device, need_bytes: int):
 
 def tc_status(device=None) -> int:
     """The status word of the tensor-core kernels (synchronises); non-zero means a bounded wait
-    ran out: in the tensor-core product 1 producer, 2 MMA issuer, 3 epilogue, 4 accumulator hand-back; in
-    attention 11/12 decode producer/consumer, 21/22 prefill producer/consumer."""
+    ran out: in the tensor-core product 1 producer, 2 MMA issuer, 3 epilogue, 4 accumulator hand-back
+    (51-54 the same by pairs of CTAs); in attention 11/12 decode producer/consumer, 21/22 prompt
+    portions on mma.sync producer/consumer; in the tcgen05 attention 31 producer, 32-36 MMA issuer
+    (query, keys, score buffer, P, -), 37-41 softmax warps (scores, last tile's values, O before a
+    rescale, P buffer, final O)."""
     out = 0
     for dev, st in _tc_state.items():
         if device is None or torch.device(device) == dev:

@@ -54,6 +54,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--shuffle-pages", action="store_true", help="attention: a request's pages lie scattered over the pool")
     a = ap.parse_args(argv)
     torch.manual_seed(0)
     dev = "cuda"
@@ -103,7 +104,8 @@ def main(argv=None) -> int:
         n_pages = rows * blocks
         kp = (torch.randn(n_pages, G, ps, hd, device=dev) * 0.5).to(bf)
         vp = (torch.randn(n_pages, G, ps, hd, device=dev) * 0.5).to(bf)
-        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(rows, blocks)
+        order = torch.randperm(n_pages, device=dev) if a.shuffle_pages else torch.arange(n_pages, device=dev)
+        table = order.to(torch.int32).view(rows, blocks).contiguous()
         T = rows * q_len
         q = torch.randn(T, H * hd, device=dev).to(bf)
         out = torch.empty(T, H * hd, dtype=bf, device=dev)
