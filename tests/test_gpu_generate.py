@@ -85,6 +85,50 @@ def test_batching_and_preemption_do_not_change_outputs(folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_of_the_sampled_ids_changes_nothing(folders, dtype):
+    """Decoding steps launched before the ids of the step before them were read (their input ids
+    stay on the device) give the same tokens as the plain loop: greedy and sampled, requests of
+    different lengths that leave the batch one by one, a stop token met in mid-flight (its
+    request has then run one step too many), and a request that arrives while others decode."""
+    from tuff_b200 import Engine, SamplingParams
+    name = "tiny_d"
+    vocab = CONFIGS[name][0]["vocab_size"]
+    prompts = [random_tokens(vocab, n, 90 + n) for n in (6, 19, 33, 11)]
+
+    def make(run_ahead):
+        return Engine(folders[name], dtype=dtype, ctx_size=160, max_tokens=1024, page_size=8, max_batched_tokens=32,
+                      max_running=8, run_ahead=run_ahead)
+
+    # a first run finds tokens that requests 0 and 2 will emit in mid-flight: they become their stop tokens
+    probe = make(False).generate(prompts, [SamplingParams(max_new_tokens=40), SamplingParams(temp=0.9, seed=3, max_new_tokens=25),
+                                           SamplingParams(max_new_tokens=33), SamplingParams(temp=1.2, top_k=12, seed=8, max_new_tokens=17)])
+    stop0, stop2 = probe[0][13], probe[2][20]
+    params = [SamplingParams(max_new_tokens=40, stop_token_ids=(stop0,)), SamplingParams(temp=0.9, seed=3, max_new_tokens=25),
+              SamplingParams(max_new_tokens=33, stop_token_ids=(stop2,)), SamplingParams(temp=1.2, top_k=12, seed=8, max_new_tokens=17)]
+    late_prompt = random_tokens(vocab, 9, 5)
+
+    def run(run_ahead):
+        eng = make(run_ahead)
+        reqs = [eng.add_request(i, p, sp) for i, (p, sp) in enumerate(zip(prompts, params))]
+        steps, late = 0, None
+        while eng.scheduler.has_work():
+            eng.step()
+            steps += 1
+            if steps == 9:
+                late = eng.add_request("late", late_prompt, SamplingParams(max_new_tokens=14))
+        eng.runner.cache.check()
+        assert not eng.runner.cache.live and eng._ahead is None
+        return [r.output for r in reqs] + [late.output], [r.finish_reason for r in reqs], eng
+
+    plain_outs, plain_why, _ = run(False)
+    ahead_outs, ahead_why, eng = run(True)
+    assert ahead_outs == plain_outs and ahead_why == plain_why
+    assert plain_why[0] == "stop" and plain_why[2] == "stop" and plain_why[1] == "length"
+    assert len(plain_outs[0]) <= 14 and plain_outs[0][-1] == stop0
+    assert eng.run_ahead and eng.timing["steps"] >= len(plain_outs[1])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_stays_on_the_plain_logits(folders, dtype):
     """300 tokens decoded one by one (pages fill up, many pages per request): the logits still
     match the whole-sequence computation at the end."""

@@ -25,11 +25,12 @@ class Engine:
     def __init__(self, model_dir: str | None, dtype="bfloat16", device="cuda:0", ctx_size: int | None = None,
                  max_tokens: int | None = None, page_size: int = 64, max_batched_tokens: int = 2048,
                  max_running: int = 64, cuda_graphs: bool = True, config: dict | None = None,
-                 weight_seed: int = 0):
+                 weight_seed: int = 0, run_ahead: bool = True):
         """ctx_size: longest request (prompt + new tokens), the command line's -c;
         max_tokens: tokens the cache pool holds over all live requests (default: ctx_size, or
         8192: one full-length request fits).  `model_dir=None` with `config` and `weight_seed`
-        builds a random-weights model on the device."""
+        builds a random-weights model on the device.  `run_ahead`: while all requests decode,
+        launch the next step before the current step's tokens have been read (see `step`)."""
         ctx = ctx_size or 8192
         self.runner = ModelRunner(model_dir, dtype=dtype, device=device,
                                   max_tokens=max_tokens if max_tokens is not None else ctx,
@@ -39,6 +40,8 @@ class Engine:
                                    max_running=max_running, max_context=self.runner.max_context)
         self.sampler = Sampler(self.runner.vocab_size, self.runner.device)
         self.timing: Dict[str, float] = dict(steps=0, step_seconds=0.0)
+        self.run_ahead = bool(run_ahead)
+        self._ahead = None            # (plan, sampled ids on the device) of a step launched and not yet read
 
     @property
     def config(self):
@@ -56,18 +59,47 @@ class Engine:
         return self.scheduler.add(request_id, prompt, params)
 
     def step(self) -> List[Request]:
-        """Plans and runs one step; returns the requests it finished."""
-        plan = self.scheduler.plan()
-        if not plan.entries:
-            return []
-        sampled = self._run(plan)
-        return self.scheduler.update(plan, sampled)
+        """Plans and runs one step; returns the requests it finished.
 
-    def _run(self, plan: StepPlan) -> List[int]:
+        While every request decodes, the step after this one is launched before this one's
+        sampled ids are read: its input ids are taken on the device from this step's result, and
+        everything else about it (positions, pages) is known.  The GPU then never waits for the
+        host to plan, lay out and launch.  The host learns the ids one step late; a request that
+        turns out to have met a stop token has run one step too many, whose result is dropped."""
+        if self._ahead is not None:
+            plan, sampled_dev = self._ahead
+            self._ahead = None
+        else:
+            plan = self.scheduler.plan()
+            if not plan.entries:
+                return []
+            sampled_dev = self._launch(plan, None)
+        nxt = None
+        if self.run_ahead and sampled_dev is not None and self._may_run_ahead(plan):
+            nxt_plan = self.scheduler.plan_ahead(plan)
+            if nxt_plan is not None:
+                nxt = (nxt_plan, self._launch(nxt_plan, sampled_dev))
+        sampled = sampled_dev.tolist() if sampled_dev is not None else []
+        finished = self.scheduler.update(plan, sampled)
+        if nxt is not None and self.scheduler.running:
+            self._ahead = nxt
+        return finished
+
+    @staticmethod
+    def _may_run_ahead(plan: StepPlan) -> bool:
+        # the repetition penalty needs the latest ids on the host before the next draw
+        return all(not (e.request.params.repeat_penalty > 1.0 and e.request.params.repeat_last_n
+                        and not e.request.params.greedy) for e in plan.entries)
+
+    def _launch(self, plan: StepPlan, token_source) -> torch.Tensor | None:
+        """Runs the plan's step and samples; returns the sampled ids, still on the device (None if
+        no entry samples).  `token_source`: the ids sampled by the step before, for a plan made
+        ahead of them."""
         t0 = time.perf_counter()
+        ahead = token_source is not None
         entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                    for e in plan.entries]
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, token_source)
         rows = []
         for e in plan.entries:
             if e.samples:
@@ -75,10 +107,8 @@ class Engine:
                 p = r.params
                 n_all = len(r.prompt) + len(r.output)
                 recent = r.token_slice(n_all - p.repeat_last_n) if (p.repeat_penalty > 1.0 and p.repeat_last_n) else ()
-                rows.append(SampleRow(p, r.key, len(r.output), recent))
-        out: List[int] = []
-        if rows:
-            out = self.sampler.sample(logits, rows).tolist()
+                rows.append(SampleRow(p, r.key, len(r.output) + (1 if ahead else 0), recent))
+        out = self.sampler.sample(logits, rows) if rows else None
         self.timing["steps"] += 1
         self.timing["step_seconds"] += time.perf_counter() - t0
         return out

@@ -97,10 +97,13 @@ class ModelRunner:
         self.cache.close(rc)
 
     # ---- the step ------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], token_source: torch.Tensor | None = None) -> torch.Tensor:
         """Runs the entries' tokens as one batch; returns fp32 logits [wanted, vocab] on the
         device, in the order of the entries and of their `want`.  Nothing is cached or
-        reserved if validation fails or the pages do not suffice (`OutOfPages`)."""
+        reserved if validation fails or the pages do not suffice (`OutOfPages`).
+        `token_source`: an int32 device tensor with one id per token of the batch that replaces
+        the entries' ids on the device (ids that an earlier step has sampled and the host has not
+        read yet); the entries then carry placeholders."""
         validate_entries(entries, self.vocab_size, self.max_context)
         done: List[StepEntry] = []
         try:
@@ -113,7 +116,7 @@ class ModelRunner:
             raise
         try:
             with torch.cuda.device(self.device):
-                logits = self._run(entries)
+                logits = self._run(entries, token_source)
         except BaseException:
             for e in entries:
                 self.cache.cancel(e.cache)
@@ -124,11 +127,13 @@ class ModelRunner:
 
     MAX_GRAPHS = 24
 
-    def _run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _run(self, entries: Sequence[StepEntry], token_source: torch.Tensor | None = None) -> torch.Tensor:
         R = len(entries)
         decode = (self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
         if not decode:
             ctx = to_device(layout_entries(entries, self.cache), self.device, self.dtype)
+            if token_source is not None:
+                ctx.tokens.copy_(token_source)
             return self.model.forward(ctx, self.cache.storages)
         # A pure decode step: the same kernels with the same shapes every time, so it is captured
         # once per number of rows (after one plain run that lets workspaces grow) and replayed.
@@ -140,6 +145,8 @@ class ModelRunner:
             self._seen_rows[R] = self._seen_rows.get(R, 0) + 1
             if self._seen_rows[R] < 2:
                 ctx = to_device(host, self.device, self.dtype)
+                if token_source is not None:
+                    ctx.tokens.copy_(token_source)
                 return self.model.forward(ctx, self.cache.storages)
             if len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
@@ -147,6 +154,8 @@ class ModelRunner:
             static = (torch.empty(n_ints, dtype=torch.int32, pin_memory=True),
                       torch.empty(n_ints, dtype=torch.int32, device=self.device), torch.cuda.Event())
             ctx = to_device(host, self.device, self.dtype, static)
+            if token_source is not None:
+                ctx.tokens.copy_(token_source)
             torch.cuda.current_stream().synchronize()
             from ..kernels import ops
             before = ops.LAUNCHES["n"]
@@ -157,7 +166,9 @@ class ModelRunner:
                                        launches=ops.LAUNCHES["n"] - before)
             ops.LAUNCHES["n"] = before                   # captured, not run: replays are counted instead
         else:
-            to_device(host, self.device, self.dtype, g["static"])
+            ctx = to_device(host, self.device, self.dtype, g["static"])
+            if token_source is not None:
+                ctx.tokens.copy_(token_source)              # into the buffer that the captured step reads
         g["graph"].replay()
         self.graph_replays += 1
         return g["logits"].clone()        # the graph's own output is overwritten by the next replay

@@ -242,6 +242,36 @@ class Scheduler:
             planned.add(id(req))
             budget -= n
 
+    def plan_ahead(self, prev: StepPlan) -> StepPlan | None:
+        """The step after `prev`, planned before `prev`'s sampled tokens are known: the same
+        requests, one more token each, the token itself still on the device (the entries carry a
+        placeholder).  Only when nothing else could happen in that step: `prev` is pure decoding,
+        nobody waits, nobody reaches its length or the context with the token that `prev` samples
+        (a stop token cannot be foreseen; `update` skips the entry of a request that met one), and
+        every request finds its page.  Otherwise None, and the next step is planned as usual."""
+        if self.waiting or not prev.entries or prev.preempted or prev.admitted:
+            return None
+        if len(prev.entries) != len(self.running):
+            return None
+        free = self._free_pages()
+        plan = StepPlan()
+        for e in prev.entries:
+            req = e.request
+            if not e.samples or len(e.tokens) != 1 or req.status is not RequestStatus.RUNNING or req.n_pending() != 0:
+                return None
+            n_out = len(req.output) + 1                       # once `prev`'s token has arrived
+            if n_out >= req.params.max_new_tokens:
+                return None
+            if self.max_context is not None and len(req.prompt) + n_out >= self.max_context:
+                return None
+            need = self.cache.pages_needed(req.cache, 1)
+            if not self._fits(need, free):
+                return None
+            self._take(need, free)
+            plan.entries.append(PlannedEntry(req, [0], True))
+        self.stats["steps"] += 1
+        return plan
+
     def _taken(self, plan: StepPlan) -> List[int]:
         """Pages that the entries planned so far will take, per group."""
         out = [0] * len(self.cache.groups)
@@ -258,6 +288,11 @@ class Scheduler:
         done: List[Request] = []
         for e in plan.entries:
             req = e.request
+            if req.status is not RequestStatus.RUNNING:
+                # planned ahead, and finished by the token before this one: its result is dropped
+                if e.samples:
+                    next(it)
+                continue
             start = req.n_cached - len(e.tokens)            # the step has run: the cache counts its tokens
             self.stats["prompt_tokens"] += max(0, min(len(req.prompt), req.n_cached) - start)
             if not e.samples:
