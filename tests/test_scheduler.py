@@ -144,3 +144,69 @@ def test_same_arrivals_same_plans():
             out.append([(e.request.request_id, tuple(e.tokens), e.samples) for e in plan.entries])
         return out
     assert trace() == trace()
+
+
+def run_ahead_loop(cm, sch, next_token):
+    """The engine's loop with steps planned ahead of the sampled tokens where the scheduler
+    allows it, without a model: returns how many steps were planned ahead."""
+    ahead, n_ahead = None, 0
+    while sch.has_work() or ahead is not None:
+        if ahead is not None:
+            plan, ahead = ahead, None
+        else:
+            plan = sch.plan()
+            for e in plan.entries:
+                cm.reserve(e.request.cache, len(e.tokens))
+                cm.commit(e.request.cache, len(e.tokens))
+        nxt = sch.plan_ahead(plan)
+        if nxt is not None:
+            n_ahead += 1
+            for e in nxt.entries:
+                assert e.tokens == [0] and e.samples and e.request.n_pending() == 0
+                cm.reserve(e.request.cache, 1)
+                cm.commit(e.request.cache, 1)
+        sampled = [next_token(e.request) for e in plan.entries if e.samples]
+        sch.update(plan, sampled)
+        cm.check()
+        if nxt is not None and sch.running:
+            ahead = nxt
+    return n_ahead
+
+
+def test_steps_planned_ahead_of_their_tokens():
+    """While everybody decodes and nothing else can happen, the next step is planned before the
+    tokens of the current one are known: not while a prompt is in portions, not while someone
+    waits, not when a request reaches its length with the pending token; a request that meets a
+    stop token in mid-flight is skipped by the step that was planned ahead; the outputs are those of
+    the plain loop."""
+    def token(req):
+        return 7 if (req.request_id == "b" and len(req.output) == 5) else 1000 + len(req.output)
+
+    def requests(sch):
+        return [sch.add("a", list(range(9)), SamplingParams(max_new_tokens=12)),
+                sch.add("b", list(range(21)), SamplingParams(max_new_tokens=20, stop_token_ids=(7,))),
+                sch.add("c", list(range(3)), SamplingParams(max_new_tokens=4))]
+
+    cm, sch = make(max_tokens=256, budget=8, max_running=4)
+    plain = requests(sch)
+    while sch.has_work():
+        run_step(cm, sch, token)
+    cm2, sch2 = make(max_tokens=256, budget=8, max_running=4)
+    ahead = requests(sch2)
+    n_ahead = run_ahead_loop(cm2, sch2, token)
+    assert [r.output for r in ahead] == [r.output for r in plain]
+    assert [r.finish_reason for r in ahead] == ["length", "stop", "length"]
+    assert n_ahead >= 4 and not cm2.live
+    # nothing is planned ahead of a prompt in portions, of a waiting request, or of a last token
+    cm3, sch3 = make(max_tokens=256, budget=8, max_running=1)
+    r1 = sch3.add("x", list(range(20)), SamplingParams(max_new_tokens=3))
+    r2 = sch3.add("y", list(range(4)), SamplingParams(max_new_tokens=2))
+    seen = []
+    while sch3.has_work():
+        plan = sch3.plan()
+        for e in plan.entries:
+            cm3.reserve(e.request.cache, len(e.tokens)); cm3.commit(e.request.cache, len(e.tokens))
+        seen.append(sch3.plan_ahead(plan) is not None)
+        sch3.update(plan, [1000 for e in plan.entries if e.samples])
+    assert not any(seen)            # "y" waits all the while "x" runs, and then "y" has two tokens to go
+    assert r1.finish_reason == r2.finish_reason == "length"
