@@ -22,42 +22,11 @@
 // never reach the result: their scores are replaced, and their values zeroed, before use,
 // so stale or never-written cache contents (even NaN) are harmless.
 // Every mbarrier wait is bounded; a wait that runs out records a code in *status.
-#include "common.cuh"
-#include <cuda.h>
-#include <cudaTypedefs.h>
-#include <mutex>
-#include <unordered_map>
+#include "sm100.cuh"
 
 namespace {
 constexpr int TILE = 64;                 // keys per tile
-constexpr uint32_t MAX_POLLS = 1u << 26;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    for (uint32_t i = 0; i < MAX_POLLS; ++i)
-        if (mbar_try(bar, parity)) return true;
-    atomicCAS(status, 0, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -71,11 +40,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
 // Address of 16-byte chunk `chunk` (8 dims) of key row `row` in a tile stored by TMA with
 // 128-byte swizzle: per 64-dim half, rows are 128 bytes apart and chunk c of row r sits at
 // c ^ (r & 7).  Halves (head size 128) are TILE*128 bytes apart.
@@ -437,54 +401,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
 }
 
 // ------------------------------------------------------------------ host side
-PFN_cuTensorMapEncodeTiled encode_fn() {
-    static PFN_cuTensorMapEncodeTiled fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (PFN_cuTensorMapEncodeTiled)f;
-    });
-    return fn;
-}
-
-struct PoolKey {
-    const void* ptr; long long rows; int hd, page_size;
-    bool operator==(const PoolKey& o) const { return ptr == o.ptr && rows == o.rows && hd == o.hd && page_size == o.page_size; }
-};
-struct PoolKeyHash {
-    size_t operator()(const PoolKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)(k.hd * 131 + k.page_size);
-    }
-};
-
-// Tensor map over a page pool seen as [num_pages * G * page_size, hd] bf16, boxes of page_size x 64.
-bool pool_map(CUtensorMap* out, const void* ptr, long long rows, int hd, int page_size) {
-    static std::unordered_map<PoolKey, CUtensorMap, PoolKeyHash> cache;
-    static std::mutex mu;
-    PoolKey key{ptr, rows, hd, page_size};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return true; }
-    PFN_cuTensorMapEncodeTiled enc = encode_fn();
-    if (!enc) return false;
-    cuuint64_t gdim[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
-    cuuint64_t gstride[1] = {(cuuint64_t)hd * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)page_size};
-    cuuint32_t estride[2] = {1, 1};
-    CUtensorMap m;
-    if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estride,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return false;
-    if (cache.size() > 1024) cache.clear();
-    cache.emplace(key, m);
-    *out = m;
-    return true;
-}
-
 bool supported(int H, int G, int hd, int page_size) {
     if (hd != 64 && hd != 128) return false;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return false;

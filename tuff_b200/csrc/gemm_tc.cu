@@ -30,11 +30,7 @@
 //
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records a code
 // in *status, lets its copies in flight land, frees its tensor memory and returns.
-#include "common.cuh"
-#include <cuda.h>
-#include <cudaTypedefs.h>
-#include <mutex>
-#include <unordered_map>
+#include "sm100.cuh"
 
 namespace {
 
@@ -42,7 +38,6 @@ constexpr int BM = 128;            // rows of the 128-row operand per CTA (UMMA 
 constexpr int BK = 64;             // K elements per stage: 128 bytes of bf16, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
-constexpr uint32_t MAX_POLLS = 1u << 26;
 
 enum : int { OUT_STORE = 0, OUT_ACCUM = 1, OUT_PARTIAL = 2, OUT_SWIGLU = 3 };
 
@@ -60,74 +55,9 @@ struct GemmParams {
     int splits;           // parts the K range is cut into
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait; on failure records `code` (first failure wins) and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    for (uint32_t i = 0; i < MAX_POLLS; ++i)
-        if (mbar_try(bar, parity)) return true;
-    atomicCAS(status, 0, code);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile [rows][64 bf16] written by TMA with 128-byte
-// swizzle: rows 128 bytes apart, groups of 8 rows 1024 bytes apart (the stride offset), version 1,
-// layout type 2 (SWIZZLE_128B).  The tile's base is 1024-byte aligned; a K step of 16 elements
-// moves the start address by 32 bytes inside the swizzled row.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major) = 16 B
-    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
-    d |= (uint64_t)1 << 46;                 // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
-    return d;
-}
-
 // Instruction descriptor: fp32 accumulator, bf16 x bf16, both K-major, M=128, N=BN.
 template <int BN> __device__ __forceinline__ constexpr uint32_t instr_desc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // Two accumulators of BN columns each, so that one is read out while the other is filled.
@@ -414,7 +344,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t a = a_tiles + s * L::A_BYTES, b = b_tiles + s * L::B_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma(acc, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
+                        umma(acc, smem_desc_k_major(a + k * UMMA_K * 2), smem_desc_k_major(b + k * UMMA_K * 2), idesc,
                              (i > 0 || k > 0) ? 1u : 0u);
                     umma_commit(empty_bar(s));      // the stage is free once these MMAs have read it
                 }
@@ -568,7 +498,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t a = a_tiles + s * L::A_BYTES, b = b_tiles + s * L::B_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_pair(acc, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        umma_pair(acc, smem_desc_k_major(a + k * UMMA_K * 2), smem_desc_k_major(b + k * UMMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(empty_bar(s));              // the stage is free in both CTAs once these MMAs have read it
                     umma_commit_pair(mapa(empty_bar(s), 1));
                 }
@@ -618,19 +548,6 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
 }
 
 // ------------------------------------------------------------------ host side
-PFN_cuTensorMapEncodeTiled encode_fn() {
-    static PFN_cuTensorMapEncodeTiled fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (PFN_cuTensorMapEncodeTiled)f;
-    });
-    return fn;
-}
-
 struct MapKey {
     const void* ptr; long long rows, cols, ld; int box_rows;
     bool operator==(const MapKey& o) const {
