@@ -128,6 +128,43 @@ def test_running_ahead_of_the_sampled_ids_changes_nothing(folders, dtype):
     assert eng.run_ahead and eng.timing["steps"] >= len(plain_outs[1])
 
 
+def test_running_ahead_under_pressure(folders):
+    """Twelve requests of random lengths arriving over time into a pool that cannot hold them all
+    (requests are preempted and recomputed), greedy and sampled: with and without steps launched
+    ahead, the same tokens, and the cache manager's books stay right."""
+    from tuff_b200 import Engine, SamplingParams
+    name = "tiny_a"
+    vocab = CONFIGS[name][0]["vocab_size"]
+    rng = np.random.default_rng(77)
+    jobs = []
+    for i in range(12):
+        n_p, n_new = int(rng.integers(1, 40)), int(rng.integers(5, 30))
+        sp = SamplingParams(max_new_tokens=n_new) if i % 3 else SamplingParams(temp=0.9, top_p=0.95, seed=10 + i, max_new_tokens=n_new)
+        jobs.append((int(rng.integers(0, 25)), random_tokens(vocab, n_p, 300 + i), sp))
+
+    def run(run_ahead):
+        eng = Engine(folders[name], dtype="float32", ctx_size=80, max_tokens=200, page_size=4, max_batched_tokens=24,
+                     max_running=6, run_ahead=run_ahead)
+        reqs, step = {}, 0
+        while len(reqs) < len(jobs) or eng.scheduler.has_work():
+            for i, (at, prompt, sp) in enumerate(jobs):
+                if at == step:
+                    eng.scheduler._next_key = i
+                    reqs[i] = eng.add_request(i, prompt, sp)
+            eng.step()
+            step += 1
+            if step % 7 == 0:
+                eng.runner.cache.check()
+        eng.runner.cache.check()
+        assert not eng.runner.cache.live
+        return [reqs[i].output for i in range(len(jobs))], eng.stats()
+
+    plain_outs, s0 = run(False)
+    ahead_outs, s1 = run(True)
+    assert plain_outs == ahead_outs
+    assert s0["preemptions"] >= 1 and all(len(o) == j[2].max_new_tokens for o, j in zip(plain_outs, jobs))
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_stays_on_the_plain_logits(folders, dtype):
     """300 tokens decoded one by one (pages fill up, many pages per request): the logits still
