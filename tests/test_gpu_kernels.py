@@ -276,10 +276,21 @@ def test_attention_prefill_tc_long_portions(H, G, page, window):
     """The tcgen05 kernel for prompt portions (head size 64): requests whose portions span several
     128-token blocks and many 64-key tiles, start inside a page and inside a tile, with and without
     a window, beside a single-token request; never-written cache slots hold NaN.  Against fp64."""
+    portions_case(H, G, page, window, (0, 70, 513, 5, 200), (300, 200, 129, 1, 128), 0)
+
+
+@pytest.mark.parametrize("H,G,page,window", [(4, 2, 16, 0), (12, 2, 8, 100), (8, 8, 64, 0)])
+def test_attention_of_decoding_rows_beside_portions(H, G, page, window):
+    """A batch as the scheduler makes it, decoding rows first and portions of prompts after them:
+    the decoding rows go to the sliced kernel and the portions to the blocked one, each with its
+    own part of the tables.  Against fp64."""
+    portions_case(H, G, page, window, (300, 70, 513, 5, 200, 64), (1, 1, 1, 140, 128, 2), 3)
+
+
+def portions_case(H, G, page, window, starts, lens, single_prefix):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(31)
     hd = 64
-    starts, lens = (0, 70, 513, 5, 200), (300, 200, 129, 1, 128)
     seqs = [a + n for a, n in zip(starts, lens)]
     kp, vp, table = paged_setup(rng, seqs, G, hd, page, "bfloat16")
     ks = [rng.normal(size=(n, G, hd)) for n in seqs]
@@ -301,7 +312,8 @@ def test_attention_prefill_tc_long_portions(H, G, page, window):
     assert ops.attention_prefill_tc_supported(q, kp, H, G, hd)
     out = torch.full((sum(lens), H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     ops.paged_attention(q, kp, vp, dev(table, torch.int32), dev(pos, torch.int32), dev(row_of, torch.int32), out, H, G, hd,
-                        1 / math.sqrt(hd), window=window, cu_q=dev(cu, torch.int32), all_single=False, max_seq_len=max(seqs))
+                        1 / math.sqrt(hd), window=window, cu_q=dev(cu, torch.int32), all_single=False, max_seq_len=max(seqs),
+                        single_prefix=single_prefix)
     ops.check_tc_status()
     o = 0
     for r, n in enumerate(lens):

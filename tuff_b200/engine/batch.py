@@ -46,6 +46,7 @@ class StepContext:
     max_q_len: int = 1                 # longest row of the step
     max_seq_len: int = 1               # longest request after the step
     all_single: bool = False           # every row brings exactly one token
+    single_prefix: int = 0             # how many leading rows bring exactly one token (decoding rows come first)
     wants_all_rows: bool = False       # the logits of every token are wanted, in token order
     host: Dict[str, object] = field(default_factory=dict)    # the same tables as NumPy arrays on the host
     extra: Dict[str, object] = field(default_factory=dict)   # room for parts defined elsewhere
@@ -111,7 +112,8 @@ def layout_entries(entries: Sequence[StepEntry], cache: CacheManager, table_widt
     return dict(tokens=tokens, positions=positions, row_of_token=row_of_token, cu_q=cu_q, slot_of_row=slot,
                 want_index=np.asarray(want, np.int32), block_tables=tables,
                 max_q_len=max(lens), max_seq_len=max(e.cache.n_tokens + n for e, n in zip(entries, lens)),
-                all_single=all(n == 1 for n in lens), wants_all_rows=want == list(range(T)))
+                all_single=all(n == 1 for n in lens), wants_all_rows=want == list(range(T)),
+                single_prefix=next((i for i, n in enumerate(lens) if n != 1), R))
 
 
 def to_device(host: dict, device: torch.device, act_dtype: torch.dtype, static=None) -> StepContext:
@@ -149,4 +151,5 @@ def to_device(host: dict, device: torch.device, act_dtype: torch.dtype, static=N
                        n_wanted=host["want_index"].size, tokens=cut[0], positions=cut[1], row_of_token=cut[2],
                        cu_q=cut[3], slot_of_row=cut[4], want_index=cut[5], block_tables=tables,
                        max_q_len=host["max_q_len"], max_seq_len=host["max_seq_len"],
-                       all_single=host["all_single"], wants_all_rows=host["wants_all_rows"], host=host)
+                       all_single=host["all_single"], wants_all_rows=host["wants_all_rows"],
+                       single_prefix=host.get("single_prefix", 0), host=host)

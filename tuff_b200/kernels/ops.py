@@ -436,9 +436,9 @@ def attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, 
 
 
 def attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
-                      window: int = 0) -> None:
+                      window: int = 0, n_tokens: int | None = None) -> None:
     """Causal attention of prompt portions (bf16): blocks of query tokens against the cached keys."""
-    n = q.shape[0]
+    n = q.shape[0] if n_tokens is None else n_tokens
     lib = load_library("attention_flash")
     st = _tc_buffers(q.device, 0)
     _check(lib.tuff_attention_prefill(_ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
@@ -463,7 +463,7 @@ def attention_prefill_tc_supported(q: torch.Tensor, k_pages: torch.Tensor, H: in
 
 
 def attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out, H, G, hd, scale,
-                         window: int = 0) -> None:
+                         window: int = 0, n_tokens: int | None = None) -> None:
     """Causal attention of prompt portions (bf16, head size 64) with tcgen05.mma: 128 query tokens
     of one head per CTA, scores and weighted values accumulated in tensor memory."""
     lib = load_library("attention_tc")
@@ -471,26 +471,39 @@ def attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out,
     _check(lib.tuff_attention_prefill_tc(_ptr(q), c_longlong(q.stride(0)), _ptr(k_pages), _ptr(v_pages),
                                          c_longlong(k_pages.shape[0]), _ptr(block_table), c_int(block_table.shape[1]),
                                          _ptr(positions), _ptr(cu_q), _ptr(out), _ptr(st["status"]),
-                                         c_int(q.shape[0]), c_int(cu_q.numel() - 1), c_int(H), c_int(G), c_int(hd),
+                                         c_int(q.shape[0] if n_tokens is None else n_tokens), c_int(cu_q.numel() - 1),
+                                         c_int(H), c_int(G), c_int(hd),
                                          c_int(k_pages.shape[2]), c_float(scale), c_int(window), _stream()),
            "attention_prefill_tc")
 
 
 def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
                     window: int = 0, ctx=None, cu_q=None, all_single: bool | None = None,
-                    max_seq_len: int | None = None) -> None:
+                    max_seq_len: int | None = None, single_prefix: int | None = None) -> None:
     """Attention over the paged cache by the kernel that suits the batch: the tensor-core kernels
-    for bf16 with head size 64 or 128 (the sliced one when every row brings a single token, the
-    blocked one otherwise), the plain kernel for everything else."""
+    for bf16 with head size 64 or 128 (the sliced one for rows that bring a single token, the
+    blocked ones for portions of prompts), the plain kernel for everything else.  `single_prefix`:
+    how many leading rows bring exactly one token; in a batch that mixes decoding rows (first) with
+    portions, each kind goes to its own kernel."""
     if ctx is not None:
         cu_q = ctx.cu_q if cu_q is None else cu_q
         all_single = ctx.all_single if all_single is None else all_single
         max_seq_len = ctx.max_seq_len if max_seq_len is None else max_seq_len
+        single_prefix = ctx.single_prefix if single_prefix is None else single_prefix
     assert q.stride(1) == 1 and out.shape == (q.shape[0], H * hd) and q.dtype == k_pages.dtype == out.dtype
+    n_rows = 0 if cu_q is None else cu_q.numel() - 1
+    sp = int(single_prefix or 0)
+    if (not all_single and cu_q is not None and 0 < sp < n_rows and attention_flash_supported(q, k_pages, H, G, hd)):
+        # decoding rows first, then portions: tokens 0..sp-1 are the decoding rows' (one each)
+        paged_attention(q[:sp], k_pages, v_pages, block_table[:sp], positions[:sp], row_of_token[:sp], out[:sp],
+                        H, G, hd, scale, window, cu_q=None, all_single=True, max_seq_len=max_seq_len, single_prefix=0)
+        # the portions keep their token numbering: q, positions and out stay whole, rows and their
+        # tables are counted from the first portion
+        _attention_portions(q, k_pages, v_pages, block_table[sp:], positions, row_of_token, cu_q[sp:], out,
+                            H, G, hd, scale, window, n_tokens=q.shape[0] - sp)
+        return
     if not all_single and cu_q is not None and attention_prefill_tc_supported(q, k_pages, H, G, hd):
-        _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
-        _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(cu_q, "cu_q")
-        attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out, H, G, hd, scale, window)
+        _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale, window)
         return
     if attention_flash_supported(q, k_pages, H, G, hd):
         _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
@@ -504,6 +517,22 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, o
                               window)
         return
     paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window)
+
+
+def _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
+                        window: int = 0, n_tokens: int | None = None) -> None:
+    """Rows of several tokens through the blocked kernels: tcgen05 where it applies, else mma.sync.
+    `cu_q` holds token numbers into q/positions/out as they are; `block_table` starts at the first
+    of these rows; `n_tokens`: how many tokens these rows bring (for sizing the launch)."""
+    _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
+    _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(cu_q, "cu_q")
+    if attention_prefill_tc_supported(q, k_pages, H, G, hd):
+        attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out, H, G, hd, scale, window,
+                             n_tokens=n_tokens)
+    else:
+        _i32(row_of_token, "row_of_token")
+        attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
+                          window, n_tokens=n_tokens)
 
 
 # -------------------------------------------------------------------- sampling
