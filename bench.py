@@ -31,11 +31,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LFM2_1P2B = dict(
-    architectures=["Lfm2ForCausalLM"], hidden_size=2048, num_hidden_layers=16, num_attention_heads=32,
-    num_key_value_heads=8, intermediate_size=8192, block_auto_adjust_ff_dim=True, block_multiple_of=256,
-    vocab_size=65536, rope_theta=1e6, norm_eps=1e-5, conv_L_cache=3, full_attn_idxs=[2, 5, 8, 10, 12, 14],
-    tie_embedding=True, max_position_embeddings=128000)
+from tuff_b200.config.lfm2 import LFM2_1P2B_SHAPE as LFM2_1P2B      # the sizes of configs[2], no weights
+
 CONTEXT = 8192
 BATCH = 8
 PREFILL_TOKENS = 2048

@@ -6,9 +6,15 @@
     python -m tuff_b200.kernels.probe attention_decode --batch 8 --context 8192
     python -m tuff_b200.kernels.probe attention_prefill --tokens 2048
 
+    python -m tuff_b200.kernels.probe decode_step --batch 8 --context 8192 --steps 6 --no-graphs
+    python -m tuff_b200.kernels.probe prefill_step --tokens 2048 --steps 3
+    python -m tuff_b200.kernels.probe mixed_step --batch 32 --context 4096 --tokens 512 --steps 5
+
 Timing: CUDA events around each launch, after warm-up, with a buffer larger than L2 written
 between launches.  Prints the median time and the achieved rate against the bytes or flops the
-kernel has to move or do.
+kernel has to move or do.  The `*_step` forms run whole steps of the engine on a random-weights
+model of the LFM2.5-1.2B sizes (contexts filled without computing them) and print the wall time a
+step; under a profiler they give the list of a step's launches.
 """
 from __future__ import annotations
 
@@ -38,9 +44,86 @@ def timed(fn, reps: int, warmup: int = 3):
     return times[len(times) // 2] * 1e-3
 
 
+def run_steps(a) -> int:
+    """Whole steps of the engine on the LFM2.5-1.2B sizes with random weights."""
+    import time
+
+    import numpy as np
+
+    from ..config.lfm2 import LFM2_1P2B_SHAPE
+    from ..engine import ModelRunner, StepEntry
+    from ..engine.engine import Engine
+    from ..engine.scheduler import RequestStatus
+    from ..sampling import SamplingParams
+    rng = np.random.default_rng(0)
+    vocab = LFM2_1P2B_SHAPE["vocab_size"]
+    if a.kernel == "decode_step":
+        n_new = a.steps + 8
+        eng = Engine(None, dtype="bfloat16", ctx_size=a.context, max_tokens=a.batch * a.context + 4096, page_size=a.page_size,
+                     max_running=a.batch, config=dict(LFM2_1P2B_SHAPE), cuda_graphs=not a.no_graphs)
+        for i in range(a.batch):
+            r = eng.scheduler.add(i, rng.integers(0, vocab, a.context - n_new).tolist(), SamplingParams(max_new_tokens=n_new))
+            eng.scheduler.waiting.remove(r)
+            r.cache = eng.runner.open(i)
+            eng.runner.synthetic_fill(r.cache, a.context - n_new - 1)
+            r.status = RequestStatus.RUNNING
+            eng.scheduler.running.append(r)
+        for _ in range(4):
+            eng.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(a.steps):
+            eng.step()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / a.steps
+        print(f"decode_step batch={a.batch} context={a.context} graphs={not a.no_graphs}: {dt * 1e3:.3f} ms a step, "
+              f"{a.batch / dt:.0f} tok/s")
+        return 0
+    if a.kernel == "prefill_step":
+        runner = ModelRunner(None, dtype="bfloat16", max_tokens=a.tokens + 4096, page_size=a.page_size, max_requests=4,
+                             max_context=a.tokens + 64, config=dict(LFM2_1P2B_SHAPE))
+        for i in range(a.steps):
+            rc = runner.open(i)
+            toks = rng.integers(0, vocab, a.tokens).tolist()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            runner.step([StepEntry(rc, toks, [a.tokens - 1])])
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t0
+            runner.close(rc)
+            print(f"prefill_step tokens={a.tokens}: {dt * 1e3:.2f} ms, {a.tokens / dt:.0f} tok/s", flush=True)
+        return 0
+    # mixed_step: decoding rows first, one portion of a prompt after them, as the scheduler lays a step out
+    ctx_max = a.context + a.tokens * (a.steps + 4) + 64
+    runner = ModelRunner(None, dtype="bfloat16", max_tokens=a.batch * (a.context + 256) + ctx_max, page_size=a.page_size,
+                         max_requests=a.batch + 1, max_context=ctx_max, config=dict(LFM2_1P2B_SHAPE))
+    rows = [runner.open(i) for i in range(a.batch)]
+    for rc in rows:
+        runner.synthetic_fill(rc, a.context)
+    portion = runner.open("portion")
+    runner.synthetic_fill(portion, a.context // 4)
+
+    def step():
+        return runner.step([StepEntry(rc, [5], [0]) for rc in rows] +
+                           [StepEntry(portion, rng.integers(0, vocab, a.tokens).tolist(), [a.tokens - 1])])
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        step()
+    torch.cuda.synchronize()
+    print(f"mixed_step {a.batch} decoding rows at {a.context} + a {a.tokens}-token portion: "
+          f"{(time.perf_counter() - t0) / a.steps * 1e3:.2f} ms a step")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_decode", "attention_decode", "attention_prefill"])
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_decode", "attention_decode", "attention_prefill",
+                                       "decode_step", "prefill_step", "mixed_step"])
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--no-graphs", action="store_true", help="decode_step: plain launches instead of CUDA graph replays")
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=11264)
     ap.add_argument("--k", type=int, default=2048)
@@ -59,6 +142,8 @@ def main(argv=None) -> int:
     torch.manual_seed(0)
     dev = "cuda"
     bf = torch.bfloat16
+    if a.kernel.endswith("_step"):
+        return run_steps(a)
 
     if a.kernel == "gemm_tc":
         x = torch.randn(a.m, a.k, device=dev).to(bf)
