@@ -116,7 +116,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
     int blk = p.n_blocks - 1 - (int)(blockIdx.x / p.H);
     int row = -1, q0 = 0, q1 = 0;
     for (int r = 0; r < p.n_rows; ++r) {
-        const int a = p.cu_q[r], b = p.cu_q[r + 1];
+        const int a = ld_act(p.cu_q + r), b = ld_act(p.cu_q + r + 1);    // written by a copy, not by the kernel before
         const int nb = (b - a + QROWS - 1) / QROWS;
         if (blk < nb) { row = r; q0 = a + blk * QROWS; q1 = b; break; }
         blk -= nb;
@@ -124,7 +124,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
     if (row < 0) return;                           // uniform over the CTA, before anything is allocated
     const int g = h / (p.H / p.G);
     const int n_here = min(QROWS, q1 - q0);
-    const int pos0 = p.positions[q0];              // positions of a request's tokens are consecutive
+    const int pos0 = ld_act(p.positions + q0);     // positions of a request's tokens are consecutive
     const int pos_last = pos0 + n_here - 1;
     const int lo_cta = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
     const int tile_lo = lo_cta / TILE, tile_hi = pos_last / TILE;
@@ -152,6 +152,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * TILE, tmem_p = tmem_o + HD;
     bool ok = true;
+    pdl_wait();                    // barriers and tensor memory are set up; queries, tables and pages are read from here on
+    pdl_launch_dependents();
 
     if (warp == 4) {
         // ---------------- producer: K and V tiles through the block table
@@ -382,6 +384,6 @@ extern "C" int tuff_attention_prefill_tc(const void* q, long long q_stride, cons
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
-    attn_prefill_tc_kernel<64><<<dim3((unsigned)(p.n_blocks * H)), NUM_THREADS, smem, stream>>>(mk, mv, p);
-    return launch_status();
+    const int rc = launch_pdl(attn_prefill_tc_kernel<64>, dim3((unsigned)(p.n_blocks * H)), dim3(NUM_THREADS), smem, stream, mk, mv, p);
+    return rc ? rc : launch_status();
 }

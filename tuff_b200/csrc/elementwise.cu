@@ -74,6 +74,7 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, Ou
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + warp;
     pdl_wait();
+    pdl_launch_dependents();                     // the next kernel may set itself up beside this one
     if (r >= n_rows) return;
     const int src = row_index ? ld_act(row_index + r) : r;
     const float* xr = x + (size_t)src * d;

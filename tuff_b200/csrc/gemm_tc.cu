@@ -157,7 +157,7 @@ __device__ __forceinline__ void load_residual(const GemmParams& p, int row0, int
         const int rr = (lane >> 2) + 8 * i;
         o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (p.mode == OUT_ACCUM && row0 + rr < p.a_rows)
-            o[i] = *(reinterpret_cast<const float4*>((const float*)p.out + (size_t)(row0 + rr) * p.ld + col0) + (lane & 3));
+            o[i] = __ldcg(reinterpret_cast<const float4*>((const float*)p.out + (size_t)(row0 + rr) * p.ld + col0) + (lane & 3));
     }
 }
 
@@ -307,6 +307,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    // Everything above touched nothing that another kernel writes: with programmatic dependent launch it
+    // runs beside the tail of the kernel before.  From here on activations are read and outputs written.
+    pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -606,8 +610,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tc_kernel<BN, STAGES><<<grid, NUM_THREADS, L::TOTAL, stream>>>(ma, mb, p);
-    return launch_status();
+    const int rc = launch_pdl(gemm_tc_kernel<BN, STAGES>, grid, dim3(NUM_THREADS), L::TOTAL, stream, ma, mb, p);
+    return rc ? rc : launch_status();
 }
 
 }  // namespace

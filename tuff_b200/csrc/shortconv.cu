@@ -109,6 +109,8 @@ shortconv_fwd_run_kernel(const bf16* __restrict__ bcx, const float* __restrict__
                          bf16* __restrict__ out, int n_tokens, int d) {
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     const int t0 = blockIdx.x * RUN;
+    pdl_wait();
+    pdl_launch_dependents();
     if (c >= d) return;
     const size_t ld = (size_t)3 * d;
     float tap[K][8];
@@ -125,32 +127,32 @@ shortconv_fwd_run_kernel(const bf16* __restrict__ bcx, const float* __restrict__
         for (int q = 0; q < 4; ++q) {
             if (tb + q < t1) {
                 const bf16* p = bcx + (size_t)(tb + q) * ld + c;
-                vb[q] = *reinterpret_cast<const uint4*>(p);
-                vc[q] = *reinterpret_cast<const uint4*>(p + d);
-                vx[q] = *reinterpret_cast<const uint4*>(p + 2 * d);
+                vb[q] = ld_act_u4(p);
+                vc[q] = ld_act_u4(p + d);
+                vx[q] = ld_act_u4(p + 2 * d);
             }
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int t = tb + q;
             if (t >= t1) break;
-            const int r = row_of_token[t];
-            const int i = t - cu_q[r];
+            const int r = ld_act(row_of_token + t);
+            const int i = t - ld_act(cu_q + r);
             if (t == t0 || i == 0) {
-                const float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+                const float* st = state + (size_t)ld_act(slot_of_row + r) * (K - 1) * d;
 #pragma unroll
                 for (int j = 0; j < K - 1; ++j) {
                     const int back = (K - 1) - j;
                     if (i - back >= 0) {
                         const bf16* p = bcx + (size_t)(t - back) * ld + c;
                         float b[8], x[8];
-                        unpack8(*reinterpret_cast<const uint4*>(p), b);
-                        unpack8(*reinterpret_cast<const uint4*>(p + 2 * d), x);
+                        unpack8(ld_act_u4(p), b);
+                        unpack8(ld_act_u4(p + 2 * d), x);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) hist[j][e] = b[e] * x[e];
                     } else {
                         const float* sp = st + (size_t)((K - 1) + (i - back)) * d + c;
-                        const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+                        const float4 s0 = __ldcg(reinterpret_cast<const float4*>(sp)), s1 = __ldcg(reinterpret_cast<const float4*>(sp + 4));
                         hist[j][0] = s0.x; hist[j][1] = s0.y; hist[j][2] = s0.z; hist[j][3] = s0.w;
                         hist[j][4] = s1.x; hist[j][5] = s1.y; hist[j][6] = s1.z; hist[j][7] = s1.w;
                     }
@@ -189,19 +191,21 @@ __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restr
                                        int d, int K) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int r = blockIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();                     // the product that follows may set itself up meanwhile
     if (c >= d) return;
-    const int q0 = cu_q[r], n = cu_q[r + 1] - q0;
+    const int q0 = ld_act(cu_q + r), n = ld_act(cu_q + r + 1) - q0;
     if (n <= 0) return;
     const size_t ld = (size_t)3 * d;
-    float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+    float* st = state + (size_t)ld_act(slot_of_row + r) * (K - 1) * d;
     for (int s = 0; s < K - 1; ++s) {
         const int i = n - (K - 1) + s;
         float u;
         if (i >= 0) {
             const T* p = bcx + (size_t)(q0 + i) * ld;
-            u = to_f32(p[c]) * to_f32(p[2 * d + c]);
+            u = ld_act(p + c) * ld_act(p + 2 * d + c);
         } else {
-            u = st[(size_t)(s + n) * d + c];
+            u = ld_act(st + (size_t)(s + n) * d + c);
         }
         st[(size_t)s * d + c] = u;
     }
@@ -258,21 +262,21 @@ extern "C" int tuff_shortconv(const void* bcx, void* out, int dtype, const float
         constexpr int RUN = 8;
         const dim3 gr(ceil_div(n_tokens, RUN), ceil_div(d / 8, threads));
         if (vec && n_tokens >= 4 * RUN && K == 3)
-            shortconv_fwd_run_kernel<3, RUN><<<gr, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row, row_of_token,
-                                                                          cu_q, (bf16*)out, n_tokens, d);
+            launch_pdl(shortconv_fwd_run_kernel<3, RUN>, gr, dim3(threads), 0, stream, (const bf16*)bcx, taps, (const float*)state, slot_of_row,
+                       row_of_token, cu_q, (bf16*)out, n_tokens, d);
         else if (vec && n_tokens >= 4 * RUN && K == 2)
-            shortconv_fwd_run_kernel<2, RUN><<<gr, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row, row_of_token,
-                                                                          cu_q, (bf16*)out, n_tokens, d);
+            launch_pdl(shortconv_fwd_run_kernel<2, RUN>, gr, dim3(threads), 0, stream, (const bf16*)bcx, taps, (const float*)state, slot_of_row,
+                       row_of_token, cu_q, (bf16*)out, n_tokens, d);
         else if (vec && n_tokens >= 4 * RUN && K == 4)
-            shortconv_fwd_run_kernel<4, RUN><<<gr, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row, row_of_token,
-                                                                          cu_q, (bf16*)out, n_tokens, d);
+            launch_pdl(shortconv_fwd_run_kernel<4, RUN>, gr, dim3(threads), 0, stream, (const bf16*)bcx, taps, (const float*)state, slot_of_row,
+                       row_of_token, cu_q, (bf16*)out, n_tokens, d);
         else if (vec)
             shortconv_fwd_vec_kernel<<<dim3(n_tokens, ceil_div(d / 8, threads)), threads, 0, stream>>>(
                 (const bf16*)bcx, taps, state, slot_of_row, row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
         else
             shortconv_fwd_kernel<bf16><<<g1, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row,
                                                                     row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
-        shortconv_state_kernel<bf16><<<g2, threads, 0, stream>>>((const bf16*)bcx, state, slot_of_row, cu_q, d, K);
+        launch_pdl(shortconv_state_kernel<bf16>, g2, dim3(threads), 0, stream, (const bf16*)bcx, state, slot_of_row, cu_q, d, K);
     } else {
         return TUFF_E_DTYPE;
     }
