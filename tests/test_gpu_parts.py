@@ -512,3 +512,85 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(tmp_path, dtype):
     got = np.concatenate(got)
     tol = 2e-4 if dtype == "float32" else 5e-2
     assert np.abs(got - ref).max() < tol, np.abs(got - ref).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_windows_have_pages_of_their_own(tmp_path, dtype):
+    """An architecture whose attention layers differ in what they keep (a window of 40 keys, all
+    keys, a window of 24): three groups of pages, each with its own block table; pages that a
+    window has passed go back to their group's pool while the request runs and are taken again by
+    the other request.  Portions, decoding and both requests in one batch, against a plain forward
+    with the same windows (head size 64: the tensor-core attention kernels in bf16)."""
+    from tuff_b200.config import Architecture, Lfm2Config, register_architecture
+    from tuff_b200.engine import ModelRunner
+    from tuff_b200.models.lfm2 import lfm2_spec
+    from tuff_b200.weights import write_random_model
+    from tiny import TINY_D
+    windows = {0: 40, 2: None, 4: 24}              # layer -> window (TINY_D: attention in layers 0, 2, 4)
+
+    def spec(cfg):
+        s = lfm2_spec(cfg)
+        s.architecture = "Lfm2Windowed"
+        for i, wdw in windows.items():
+            s.layers[i].mixer.params["window"] = wdw
+        return s
+    register_architecture(Architecture("Lfm2Windowed", Lfm2Config.from_dict, spec, lambda c: c.to_dict()))
+    folder = write_random_model(str(tmp_path / "windowed"), dict(TINY_D, architectures=["Lfm2Windowed"]), 8)
+    m = plain.PlainLfm2(folder)
+    w, d, eps = m.w, m.d, m.eps
+
+    def plain_forward(tokens):
+        x = plain.embed(w["model.embed_tokens.weight"], tokens)
+        for i in range(5):
+            p = f"model.layers.{i}."
+            h = plain.rms_norm(x, w[p + "operator_norm.weight"], eps)
+            if i in windows:
+                a = p + "self_attn."
+                o = plain.gqa_attention_mixer(h, w[a + "q_proj.weight"], w[a + "k_proj.weight"], w[a + "v_proj.weight"],
+                                              w[a + "out_proj.weight"], w[a + "q_layernorm.weight"], w[a + "k_layernorm.weight"],
+                                              m.H, m.G, m.hd, eps, m.theta, window=windows[i])
+            else:
+                o = plain.short_conv_mixer(h, w[p + "conv.in_proj.weight"], w[p + "conv.conv.weight"].reshape(d, 3),
+                                           w[p + "conv.out_proj.weight"])
+            x = x + o
+            f = p + "feed_forward."
+            x = x + plain.swiglu_ffn(plain.rms_norm(x, w[p + "ffn_norm.weight"], eps), w[f + "w1.weight"],
+                                     w[f + "w3.weight"], w[f + "w2.weight"])
+        return plain.lm_head(x, w["model.embedding_norm.weight"], eps, w["model.embed_tokens.weight"])
+
+    runner = ModelRunner(folder, dtype=dtype, max_tokens=256, page_size=8, max_requests=2)
+    cm = runner.cache
+    assert sorted(str(g.need.window) for g in cm.groups) == ["24", "40", "None"]
+    rng = np.random.default_rng(6)
+    seqs = {"a": rng.integers(0, 500, 150).tolist(), "b": rng.integers(0, 500, 90).tolist()}
+    refs = {k: plain_forward(v) for k, v in seqs.items()}
+    rcs = {"a": runner.open("a")}
+    tol = 3e-4 if dtype == "float32" else 6e-2
+    worst = 0.0
+
+    def run(entries):
+        nonlocal worst
+        logits = f64(runner.step([StepEntry(rcs[k], seqs[k][lo:hi], list(range(hi - lo))) for k, lo, hi in entries]))
+        o = 0
+        for k, lo, hi in entries:
+            worst = max(worst, np.abs(logits[o:o + hi - lo] - refs[k][lo:hi]).max())
+            o += hi - lo
+        cm.check()
+
+    run([("a", 0, 33)])
+    run([("a", 33, 97)])                            # the window of 40 has passed the first pages: they are free again
+    free_after_prompt = {str(g.need.window): g.pool.n_free for g in cm.groups}
+    assert free_after_prompt["40"] > free_after_prompt["None"] and free_after_prompt["24"] > free_after_prompt["40"]
+    rcs["b"] = runner.open("b")
+    run([("a", 97, 98), ("b", 0, 50)])              # a decoding row beside a portion
+    pos = {"a": 98, "b": 50}
+    while pos["a"] < 150 or pos["b"] < 90:
+        entries = [(k, pos[k], pos[k] + 1) for k in ("a", "b") if pos[k] < len(seqs[k])]
+        run(entries)
+        for k, lo, hi in entries:
+            pos[k] = hi
+    assert worst < tol, worst
+    held = {str(g.need.window): sum(p != -1 for p in rcs["a"].tables[i]) for i, g in enumerate(cm.groups)}
+    assert held["None"] == 19 and held["40"] <= 6 and held["24"] <= 4        # 150 tokens in pages of 8; windows keep a few
+    runner.close(rcs["a"]); runner.close(rcs["b"])
+    cm.check()
