@@ -56,7 +56,7 @@ def test_rmsnorm(dtype, d, n, eps):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(1, 301, 80), (7, 130, 200), (65, 64, 48), (130, 257, 1000), (3, 2048, 5632),
-                                   (300, 520, 136), (512, 2048, 192), (257, 129, 72), (1100, 777, 2048)])
+                                   (300, 520, 136), (512, 2048, 192), (257, 129, 72), (1100, 777, 2048), (2048, 3080, 136)])
 def test_linear(dtype, M, N, K):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(2)

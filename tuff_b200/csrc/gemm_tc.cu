@@ -672,6 +672,9 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         if (bn == 256 && !swiglu) {
             const int rows = ceil_div(M, BM);
             if (rows * ceil_div(N, 256) <= 74) bn = 128;
+            else if (ceil_div(rows * ceil_div(N, 192), 148) * 192 < ceil_div(rows * ceil_div(N, 256), 148) * 256) bn = 192;
+            // 192-wide tiles when they fill the rounds of the SMs better: 2,048 x 3,072 takes two rounds either
+            // way (192 tiles of 256 columns, 256 of 192), and two rounds of narrower tiles are shorter
         }
         p.a_rows = M; p.b_rows = N;
         if (!tensor_map(&ma, A, M, K, lda, BM) || !tensor_map(&mb, W, N, K, ldw, bn)) return TUFF_E_ALIGN;
@@ -704,6 +707,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         case 32: rc = launch<32, 8>(ma, mb, p, grid, stream); break;
         case 64: rc = launch<64, 6>(ma, mb, p, grid, stream); break;
         case 128: rc = launch<128, 5>(ma, mb, p, grid, stream); break;
+        case 192: rc = launch<192, 5>(ma, mb, p, grid, stream); break;
         default: rc = launch<256, 4>(ma, mb, p, grid, stream); break;
     }
     if (rc != 0 || splits == 1) return rc;
