@@ -19,8 +19,6 @@ import os
 import sys
 from typing import Dict, IO
 
-import numpy as np
-
 from ..cache.manager import RequestCache
 from .batch import StepEntry
 from .runner import ModelRunner

@@ -18,7 +18,7 @@ from ..config.registry import config_from_dict, load_config
 from ..models.model import Model
 from ..weights.loader import load_checkpoint
 from ..weights.random_init import random_device_tensors
-from .batch import BatchError, StepContext, StepEntry, layout_entries, to_device, validate_entries
+from .batch import StepEntry, layout_entries, to_device, validate_entries
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 

@@ -7,7 +7,6 @@ raises (`tuff_b200.kernels.build.KernelBuildError`).
 """
 from __future__ import annotations
 
-import ctypes
 import os
 import struct
 from ctypes import c_float, c_int, c_longlong, c_void_p
