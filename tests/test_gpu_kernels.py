@@ -285,12 +285,13 @@ def test_attention_of_decoding_rows_beside_portions(H, G, page, window):
     the decoding rows go to the sliced kernel and the portions to the blocked one, each with its
     own part of the tables.  Against fp64."""
     portions_case(H, G, page, window, (300, 70, 513, 5, 200, 64), (1, 1, 1, 140, 128, 2), 3)
+    # head size 128: the sliced kernel beside the blocked mma.sync kernel
+    portions_case(H, G, page, window, (300, 70, 513, 5, 200, 64), (1, 1, 1, 140, 128, 2), 3, hd=128)
 
 
-def portions_case(H, G, page, window, starts, lens, single_prefix):
+def portions_case(H, G, page, window, starts, lens, single_prefix, hd=64):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(31)
-    hd = 64
     seqs = [a + n for a, n in zip(starts, lens)]
     kp, vp, table = paged_setup(rng, seqs, G, hd, page, "bfloat16")
     ks = [rng.normal(size=(n, G, hd)) for n in seqs]
@@ -309,7 +310,7 @@ def portions_case(H, G, page, window, starts, lens, single_prefix):
     pos = np.concatenate([np.arange(a, a + n) for a, n in zip(starts, lens)])
     row_of = np.repeat(np.arange(len(lens)), lens)
     cu = np.concatenate([[0], np.cumsum(lens)])
-    assert ops.attention_prefill_tc_supported(q, kp, H, G, hd)
+    assert ops.attention_prefill_tc_supported(q, kp, H, G, hd) == (hd == 64)
     out = torch.full((sum(lens), H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     ops.paged_attention(q, kp, vp, dev(table, torch.int32), dev(pos, torch.int32), dev(row_of, torch.int32), out, H, G, hd,
                         1 / math.sqrt(hd), window=window, cu_q=dev(cu, torch.int32), all_single=False, max_seq_len=max(seqs),
