@@ -433,6 +433,57 @@ def test_gemm_decode_epilogues_and_fused_norm(M, N, K):
     close(out, ref, "bfloat16")
 
 
+@pytest.mark.parametrize("M,d,K,N2", [(8, 2048, 2048, 6144), (1, 2048, 5632, 2048), (13, 264, 96, 520), (5, 1000, 80, 301),
+                                     (16, 2048, 8192, 2048)])
+def test_gemm_decode_norm_split_over_two_products(M, d, K, N2):
+    """A product that adds into the residual prepares the RMSNorm that follows (bf16(x * w) and sums of
+    squares per CTA), and the product that consumes the norm scales its rows: against fp64, with
+    epilogues store and swiglu; the preparation is dropped when x is written again."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(24)
+    a = dev(rng.normal(size=(M, K)), torch.bfloat16)
+    w1 = dev(rng.normal(size=(d, K)) * 0.05, torch.bfloat16)
+    x0 = dev(rng.normal(size=(M, d)) * 2)
+    nw = dev(1 + 0.1 * rng.normal(size=d))
+    w2 = dev(rng.normal(size=(N2, d)) * 0.05, torch.bfloat16)
+    eps = 1e-5
+    x = x0.clone()
+    ops.announce_norm(x, nw, eps)
+    ops.linear(a, w1, x, accumulate=True)
+    x_ref = x0.double().cpu().numpy() + a.double().cpu().numpy() @ w1.double().cpu().numpy().T
+    close(x, x_ref, "float32", scale=4.0)
+    lazy = ops.NormedRows(x, nw, eps, torch.bfloat16)
+    assert lazy.pre is not None and lazy.fusable(w2)
+    x64 = x.double().cpu().numpy()
+    h = x64 / np.sqrt((x64 ** 2).mean(-1, keepdims=True) + eps) * nw.double().cpu().numpy()
+    ref = h @ w2.double().cpu().numpy().T
+    out = torch.full((M, N2), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear(lazy, w2, out)
+    close(out, ref, "bfloat16", scale=1.5)
+    if N2 % 2 == 0:
+        F = N2 // 2
+        act = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ops.linear_swiglu(lazy, w2, act)
+        gu = torch.as_tensor(ref).to(torch.bfloat16).double().numpy()
+        close(act, gu[:, :F] / (1 + np.exp(-gu[:, :F])) * gu[:, F:], "bfloat16", scale=2.0)
+    # the same norm computed by the product itself (nothing prepared) agrees
+    if K <= ops.FUSED_NORM_MAX_K or True:
+        plain_h = torch.empty(M, d, dtype=torch.bfloat16, device="cuda")
+        ops.rmsnorm(x, nw, eps, plain_h)
+        out2 = torch.empty(M, N2, dtype=torch.bfloat16, device="cuda")
+        ops.linear(plain_h, w2, out2)
+        close(out2, ref, "bfloat16", scale=1.5)
+    # written again by a kernel of this module, or in place by torch: the preparation is void
+    ops.linear(a, w1, x, accumulate=True)
+    assert ops.NormedRows(x, nw, eps, torch.bfloat16).pre is None
+    ops.announce_norm(x, nw, eps)
+    ops.linear(a, w1, x, accumulate=True)
+    assert ops.NormedRows(x, nw, eps, torch.bfloat16).pre is not None
+    x.add_(1.0)
+    assert ops.NormedRows(x, nw, eps, torch.bfloat16).pre is None
+    ops.check_tc_status()
+
+
 @pytest.mark.parametrize("M,F,K", [(1, 100, 80), (8, 5632, 2048), (16, 264, 96), (7, 40, 64)])
 def test_gemm_decode_swiglu(M, F, K):
     from tuff_b200.kernels import ops

@@ -425,8 +425,9 @@ extern "C" int tuff_attention_decode_splits(int n_tokens, int G, int max_seq_len
     if (const char* e = getenv("TUFF_ATTN_SPLITS")) { const int v = atoi(e); if (v > 0) return v < tiles ? v : tiles; }
     // Enough CTAs to cover the SMs twice; beyond what stays resident at once (three CTAs per SM),
     // a count that fills whole rounds: a last round that is nearly empty costs a full round.
-    const int pairs = n_tokens * G, resident = 3 * 148;
-    int want = (2 * 148 + pairs - 1) / pairs;
+    const int sms = sm_count();
+    const int pairs = n_tokens * G, resident = 3 * sms;
+    int want = (2 * sms + pairs - 1) / pairs;
     if (pairs * want > resident) {
         int best = want;
         double best_eff = 0.0;

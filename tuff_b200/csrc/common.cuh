@@ -119,3 +119,16 @@ static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Number of SMs of the current device (asked once per device): grids of persistent CTAs are sized by it.
+static inline int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!cached[dev]) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 1;
+        cached[dev] = v;
+    }
+    return cached[dev];
+}

@@ -8,6 +8,7 @@
 // The kernels themselves are written for bf16/fp32 activations on sm_100a; the
 // reference's are Q8_1/Q4_K kernels for sm_86.
 #include "common.cuh"
+#include <algorithm>
 
 // ---------------------------------------------------------------- embedding
 template <typename WT>
@@ -161,7 +162,8 @@ extern "C" int tuff_swiglu(const void* gu, void* out, int dtype, int n_tokens, i
     if (F % blk) return TUFF_E_SIZE;
     const size_t total = (size_t)n_tokens * F;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const size_t cap = (size_t)sm_count() * 16;
+    const int blocks = (int)std::min((total + threads - 1) / threads, cap);
     if (dtype == TUFF_F32) swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, n_tokens, F, blk);
     else if (dtype == TUFF_BF16) swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, n_tokens, F, blk);
     else return TUFF_E_DTYPE;
@@ -179,7 +181,7 @@ extern "C" int tuff_cast(const void* in, int in_dtype, void* out, int out_dtype,
     if (n <= 0) return 0;
     const int threads = 256;
     long long want = (n + threads - 1) / threads;
-    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const int blocks = (int)std::min(want, (long long)sm_count() * 16);
     if (in_dtype == TUFF_F32 && out_dtype == TUFF_BF16) cast_kernel<float, bf16><<<blocks, threads, 0, stream>>>((const float*)in, (bf16*)out, (size_t)n);
     else if (in_dtype == TUFF_BF16 && out_dtype == TUFF_F32) cast_kernel<bf16, float><<<blocks, threads, 0, stream>>>((const bf16*)in, (float*)out, (size_t)n);
     else return TUFF_E_DTYPE;

@@ -20,17 +20,10 @@
 // quantised weights (src/lfm25_gpu.cu:148-202, 860-934); accumulation into the
 // residual is its accum=true (src/lfm25_engine.c:380,405,419).
 //
-// With many tokens and a wide output the tiles are computed by pairs of CTAs on the two SMs of
-// a TPC (a cluster of two, tcgen05.mma.cta_group::2): the pair computes 256 rows x 256 columns,
-// each CTA holds its own 128 rows of A and one half of the 256 rows of W, and the tensor cores
-// of both SMs read both halves.  A CTA thus streams 32 KB per K block instead of 48 KB for the
-// same amount of arithmetic per SM.  No copy is multicast: each CTA loads what it holds,
-// signalling the first CTA's barrier.  Measured, the pairs are no faster than single CTAs on
-// the shapes of this model, so they are an option (TUFF_GEMM_PAIR=1), not the default.
-//
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records a code
 // in *status, lets its copies in flight land, frees its tensor memory and returns.
 #include "sm100.cuh"
+#include <algorithm>
 
 namespace {
 
@@ -384,155 +377,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
-// ------------------------------------------------------------------ pairs of CTAs (cta_group::2)
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// The address, in the cluster's shared window, of the same location in CTA `rank`.
-__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// A tile into this CTA's shared memory; the bytes are counted on a barrier that may lie in the other CTA.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
-}
-
-constexpr int PAIR_BN = 256;
-constexpr int PAIR_STAGES = 6;
-struct PairSmem {
-    static constexpr int A_BYTES = BM * BK * 2;                  // this CTA's 128 rows of A
-    static constexpr int B_BYTES = (PAIR_BN / 2) * BK * 2;       // this CTA's half of the 256 rows of W
-    static constexpr int TILES = PAIR_STAGES * (A_BYTES + B_BYTES);
-    static constexpr int BARS = TILES;                           // full[S], empty[S], acc_full[2], acc_empty[2]
-    static constexpr int TMEM_SLOT = BARS + (2 * PAIR_STAGES + 4) * 8;
-    static constexpr int OUT_STAGE = TMEM_SLOT + 16;
-    static constexpr int TOTAL = OUT_STAGE + 4 * 2048 + 1024;
-};
-
-// Work item w of a pair: 256 rows of A (this CTA: 128 of them) x 256 rows of W.  The first CTA of
-// the pair issues the MMAs for both; everything else (loads of its own operand parts, epilogue of
-// its own 128 rows out of its own tensor memory) each CTA does for itself.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
-    using L = PairSmem;
-    constexpr int BN = PAIR_BN, STAGES = PAIR_STAGES;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t a_tiles = base, b_tiles = base + STAGES * L::A_BYTES;
-    const uint32_t bars = base + L::BARS;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
-    auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::TMEM_SLOT);
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();                     // 0: issues the MMAs
-    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int mt = (p.a_rows + 2 * BM - 1) / (2 * BM), nt = (p.b_rows + BN - 1) / BN;
-    const int n_work = mt * nt;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 8); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {      // the same warp of both CTAs takes part in the allocation
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(base + (uint32_t)L::TMEM_SLOT), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync();                                              // both CTAs' barriers exist before either signals the other
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    bool ok = true;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int w = pair; w < n_work && ok; w += n_pairs) {
-                const int m0 = (w % mt) * 2 * BM + (int)rank * BM, n0 = (w / mt) * BN + (int)rank * (BN / 2);
-                for (int i = 0; i < p.k_blocks; ++i, ++it) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(empty_bar(s), ((it / STAGES) & 1u) ^ 1u, p.status, 51)) { ok = false; break; }
-                    // the first CTA's barrier counts the bytes of both CTAs
-                    if (rank == 0) mbar_expect_tx(full_bar(s), 2 * (L::A_BYTES + L::B_BYTES));
-                    const uint32_t fb = mapa(full_bar(s), 0);
-                    tma_load_2d_pair(a_tiles + s * L::A_BYTES, &map_a, fb, i * BK, m0);
-                    tma_load_2d_pair(b_tiles + s * L::B_BYTES, &map_b, fb, i * BK, n0);
-                }
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
-            // M = 256 over the pair, N = 256
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-            uint32_t it = 0, tile = 0;
-            for (int w = pair; w < n_work && ok; w += n_pairs, ++tile) {
-                const uint32_t buf = tile & 1u;
-                if (!mbar_wait(acc_empty(buf), ((tile >> 1) & 1u) ^ 1u, p.status, 54)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t acc = tmem_base + buf * BN;
-                for (int i = 0; i < p.k_blocks; ++i, ++it) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(full_bar(s), (it / STAGES) & 1u, p.status, 52)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a = a_tiles + s * L::A_BYTES, b = b_tiles + s * L::B_BYTES;
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_pair(acc, smem_desc_k_major(a + k * UMMA_K * 2), smem_desc_k_major(b + k * UMMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-                    umma_commit_pair(empty_bar(s));              // the stage is free in both CTAs once these MMAs have read it
-                    umma_commit_pair(mapa(empty_bar(s), 1));
-                }
-                if (ok) { umma_commit_pair(acc_full(buf)); umma_commit_pair(mapa(acc_full(buf), 1)); }
-            }
-        }
-    } else {
-        const int quad = warp & 3;
-        uint32_t tile = 0;
-        for (int w = pair; w < n_work && ok; w += n_pairs, ++tile) {
-            const int m0 = (w % mt) * 2 * BM + (int)rank * BM, n0 = (w / mt) * BN;
-            const uint32_t buf = tile & 1u;
-            if (!mbar_wait(acc_full(buf), (tile >> 1) & 1u, p.status, 53)) { ok = false; break; }
-            tc_fence_after();
-            write_tile<BN>(p, base_ptr + L::OUT_STAGE + (warp - 2) * 2048, tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN,
-                           m0, n0, 0, quad, lane);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa(acc_empty(buf), 0));      // the MMA thread sits in the first CTA
-        }
-    }
-    if (!ok) for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync();                                              // neither CTA leaves while the other may still use its memory
-    if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-    }
-}
-
 // Adds the split-K partial sums in split order and writes them out.
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, long long ld,
                                      int n_tok, int n_out, int splits, int mode, int out_dtype) {
@@ -592,15 +436,6 @@ bool tensor_map(CUtensorMap* out, const void* ptr, long long rows, long long col
     return true;
 }
 
-// Off unless TUFF_GEMM_PAIR=1: measured at 2,048 tokens on the 1.2B shapes and at 8192^3, the
-// pairs ran within 2% of single CTAs (50.1 against 49.3 us for 2048 x 6144 x 2048, 1,373 against
-// 1,380 TFLOP/s at 8192^3), so the simpler kernel stays the default.
-bool pair_enabled() {
-    static int on = -1;
-    if (on < 0) { const char* e = getenv("TUFF_GEMM_PAIR"); on = (e && e[0] == '1') ? 1 : 0; }
-    return on == 1;
-}
-
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
@@ -646,6 +481,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TUFF_E_ALIGN;
     const int k_blocks = ceil_div(K, BK);
     const bool swapped = M <= 128;
+    const int sms = sm_count();
     GemmParams p{};
     p.out = C; p.partial = workspace; p.status = status; p.ld = ldc; p.k_blocks = k_blocks;
     p.out_dtype = c_dtype; p.swapped = swapped ? 1 : 0;
@@ -656,8 +492,8 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
         p.a_rows = N; p.b_rows = M;
         const int tiles = ceil_div(N, BM);
-        if (tiles < 148 && k_blocks > 1) {
-            splits = 148 / tiles > 0 ? 148 / tiles : 1;     // one wave of work items: fewer, larger items
+        if (tiles < sms && k_blocks > 1) {
+            splits = sms / tiles > 0 ? sms / tiles : 1;     // one wave of work items: fewer, larger items
             if (splits > 16) splits = 16;
             if (splits > k_blocks) splits = k_blocks;
             const long long need = (long long)splits * M * N * 4;
@@ -671,28 +507,13 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         // at 544 x 2,048 x 2,048: 30.7 us with 128 x 256 tiles (40 of them), 22.5 us with 128 x 128.
         if (bn == 256 && !swiglu) {
             const int rows = ceil_div(M, BM);
-            if (rows * ceil_div(N, 256) <= 74) bn = 128;
-            else if (ceil_div(rows * ceil_div(N, 192), 148) * 192 < ceil_div(rows * ceil_div(N, 256), 148) * 256) bn = 192;
+            if (rows * ceil_div(N, 256) <= sms / 2) bn = 128;
+            else if (ceil_div(rows * ceil_div(N, 192), sms) * 192 < ceil_div(rows * ceil_div(N, 256), sms) * 256) bn = 192;
             // 192-wide tiles when they fill the rounds of the SMs better: 2,048 x 3,072 takes two rounds either
             // way (192 tiles of 256 columns, 256 of 192), and two rounds of narrower tiles are shorter
         }
         p.a_rows = M; p.b_rows = N;
         if (!tensor_map(&ma, A, M, K, lda, BM) || !tensor_map(&mb, W, N, K, ldw, bn)) return TUFF_E_ALIGN;
-    }
-    if (!swapped && bn == 256 && M >= 256 && pair_enabled()) {
-        // pairs of CTAs: 256 x 256 tiles, W loaded in two halves of 128 rows
-        if (!tensor_map(&mb, W, N, K, ldw, PAIR_BN / 2)) return TUFF_E_ALIGN;
-        p.kb_per_split = k_blocks; p.splits = 1;
-        const int work = ceil_div(M, 2 * BM) * ceil_div(N, PAIR_BN);
-        static bool configured = false;
-        if (!configured) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL);
-            if (e != cudaSuccess) return (int)e;
-            configured = true;
-        }
-        const int pairs = work < 74 ? work : 74;
-        gemm_tc_pair_kernel<<<dim3(2 * pairs), NUM_THREADS, PairSmem::TOTAL, stream>>>(ma, mb, p);
-        return launch_status();
     }
     p.kb_per_split = ceil_div(k_blocks, splits);
     splits = ceil_div(k_blocks, p.kb_per_split);
@@ -700,7 +521,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     if (splits > 1) p.mode = OUT_PARTIAL;
     p.splits = splits;
     const int n_work = ceil_div(p.a_rows, BM) * ceil_div(p.b_rows, bn) * splits;
-    dim3 grid(n_work < 148 ? n_work : 148);
+    dim3 grid(n_work < sms ? n_work : sms);
     int rc;
     switch (bn) {
         case 16: rc = launch<16, 8>(ma, mb, p, grid, stream); break;
@@ -713,7 +534,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     if (rc != 0 || splits == 1) return rc;
     const size_t total = (size_t)M * N;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads : 148 * 8);
+    const int blocks = (int)std::min((total + threads - 1) / threads, (size_t)sms * 8);
     splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(workspace, C, ldc, M, N, splits, user_mode, c_dtype);
     return launch_status();
 }

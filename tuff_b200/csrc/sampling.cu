@@ -353,7 +353,7 @@ extern "C" long long tuff_argmax_scratch_bytes(int n_rows) { return (long long)n
 extern "C" int tuff_argmax(const float* logits, int n_rows, int V, int* out, void* scratch, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V < 1) return TUFF_E_SIZE;
-    if (scratch && V >= 8192 && n_rows * 4 <= 2 * 148) {
+    if (scratch && V >= 8192 && n_rows * 4 <= 2 * sm_count()) {
         float* pv = (float*)scratch;
         int* pi = (int*)(pv + (size_t)n_rows * ARGMAX_PARTS);
         unsigned* cnt = (unsigned*)(pi + (size_t)n_rows * ARGMAX_PARTS);

@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import os
 import struct
+import weakref
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -76,6 +77,7 @@ def _i32(t: torch.Tensor | None, name: str) -> None:
 # ----------------------------------------------------------------- elementwise
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, :] = table[tokens[t], :] as float32."""
+    _written(out)
     _i32(tokens, "tokens")
     n, d = out.shape
     assert out.dtype == torch.float32 and table.shape[1] == d and tokens.numel() == n
@@ -88,6 +90,7 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             row_index: torch.Tensor | None = None) -> None:
     """out[r] = x[row_index[r] or r] * rsqrt(mean(x^2) + eps) * weight."""
+    _written(out)
     d = x.shape[-1]
     n = out.shape[0]
     assert weight.dtype == torch.float32 and weight.numel() == d and out.shape[-1] == d
@@ -100,6 +103,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
     """out = silu(gate) * up.  gate_up [n, 2F] holds, per `block` outputs, block gate columns then
     block up columns; block = 0 means all F gate columns, then all F up columns."""
+    _written(out)
     n, F = out.shape
     assert gate_up.shape == (n, 2 * F) and gate_up.dtype == out.dtype
     _contig(gate_up, "gate_up"); _contig(out, "out")
@@ -122,6 +126,7 @@ def stack_gate_up(w1: torch.Tensor, w3: torch.Tensor, block: int = 128):
 
 def cast(src: torch.Tensor, out: torch.Tensor) -> None:
     assert src.numel() == out.numel()
+    _written(out)
     _contig(src, "src"); _contig(out, "out")
     lib = load_library("elementwise")
     _check(lib.tuff_cast(_ptr(src), dtype_code(src), _ptr(out), dtype_code(out), c_longlong(src.numel()), _stream()),
@@ -131,6 +136,7 @@ def cast(src: torch.Tensor, out: torch.Tensor) -> None:
 # ------------------------------------------------------------------------ GEMM
 def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (=|+=) a @ w.T with fp32 FFMA accumulation; a [M,K], w [N,K], out [M,N]."""
+    _written(out)
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.shape == (M, N)
@@ -188,6 +194,7 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumu
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, swiglu: bool = False) -> None:
     """out (=|+=) a @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation).  `swiglu`:
     w is a gate/up matrix in blocks of 128 (see stack_gate_up) and out [M, F] = silu(gate) * up."""
+    _written(out)
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.shape == (M, N // 2 if swiglu else N)
@@ -209,15 +216,63 @@ SKINNY_MAX_TOKENS = 16
 FUSED_NORM_MAX_K = 2048          # the widest row the fused RMSNorm of a decode product holds in registers
 
 
+# ---- a norm split over the products around it -------------------------------------------------
+# A decode product that adds into the residual x can also write what the RMSNorm that follows needs
+# (csrc/gemm_stream.cu, "emit"): bf16(x * weight) and sums of squares per CTA.  The product that
+# consumes the norm then reads those rows and scales its result rows, and no CTA norms x itself.
+# `announce_norm` says which norm will follow the next addition into x; the product that performs
+# it leaves a record here; `NormedRows` picks the record up if x has not been written since
+# (every op of this module that writes a tensor drops the tensor's record, and a torch in-place
+# operation changes x._version).
+_norm_announced: dict = {}
+_norm_ready: dict = {}
+# What a decode product writes for another decode product to read as its activations, it writes
+# FANOUT times ([FANOUT, M, N]), and each CTA of the reader takes one copy: all CTAs need all of it
+# at the same moment, and 148 requests for the same few lines wait for one another in L2.
+FANOUT = max(1, int(os.environ.get("TUFF_STREAM_COPIES", "8")))
+_fanout: dict = {}
+
+
+def announce_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """The next decode product that adds into `x` (fp32 [M, d], M <= 16) may prepare RMSNorm(x; weight, eps)."""
+    if (GEMM_STREAM and x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= SKINNY_MAX_TOKENS
+            and x.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == x.shape[1]):
+        _norm_announced[x.data_ptr()] = (weight, float(eps))
+
+
+def _written(t: torch.Tensor) -> None:
+    """`t` is about to be written by a kernel of this module: what was prepared from its old values is void."""
+    if _norm_announced or _norm_ready or _fanout:
+        ptr = t.data_ptr()
+        _norm_announced.pop(ptr, None)
+        _norm_ready.pop(ptr, None)
+        _fanout.pop(ptr, None)
+
+
+def _remember(table: dict, t: torch.Tensor, rec: dict) -> None:
+    """Files `rec` under tensor `t`: valid while this very tensor object lives unchanged (a new tensor may
+    get the same address)."""
+    if len(table) > 64:
+        for k in [k for k, r in table.items() if r["ref"]() is None]:
+            del table[k]
+    rec["ref"], rec["version"] = weakref.ref(t), t._version
+    table[t.data_ptr()] = rec
+
+
 class NormedRows:
     """An RMSNorm that has not run yet: `x` (fp32 [M, d]) to be normed with `weight` and `eps` into
-    `dtype`.  The decode products take it as their input and norm the rows themselves; anything
+    `dtype`.  The decode products take it as their input and norm the rows themselves (or, when the
+    product that last added into x prepared the norm, read the prepared rows: `pre`); anything
     else calls `dense()` and gets the normed tensor (computed once)."""
 
     def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float, dtype: torch.dtype):
         self.x, self.weight, self.eps, self.dtype = x, weight, float(eps), dtype
         self.shape, self.device = x.shape, x.device
         self._dense = None
+        rec = _norm_ready.get(x.data_ptr()) if _norm_ready else None
+        self.pre = rec if (rec is not None and rec["ref"]() is x and rec["weight"].data_ptr() == weight.data_ptr() and rec["eps"] == self.eps
+                           and rec["shape"] == tuple(x.shape) and rec["version"] == x._version
+                           and dtype == torch.bfloat16) else None
 
     def dense(self) -> torch.Tensor:
         if self._dense is None:
@@ -227,12 +282,16 @@ class NormedRows:
 
     def fusable(self, w: torch.Tensor) -> bool:
         M, K = self.x.shape
+        if self.pre is not None:
+            return (w.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS and K % 8 == 0 and w.stride(0) % 8 == 0
+                    and w.stride(1) == 1 and w.data_ptr() % 16 == 0)
         return (self.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS
                 and K % 8 == 0 and K <= FUSED_NORM_MAX_K and w.stride(0) % 8 == 0 and w.stride(1) == 1
                 and w.data_ptr() % 16 == 0 and self.x.is_contiguous() and self.x.data_ptr() % 16 == 0)
 
 
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_CONV = 0, 1, 2, 3
+GEMM_STREAM = os.environ.get("TUFF_GEMM_STREAM", "1") != "0"
 
 
 def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, conv=None, set_block: int = 0) -> None:
@@ -240,7 +299,17 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
     `a` is a bf16 tensor [M, K] or a `NormedRows`; epilogue EPI_SWIGLU takes w = [gate; up] stacked,
     EPI_CONV takes w = [B; C; x] stacked and conv = (taps [d, L], state [slots, L-1, d], slot_of_row)."""
     norm = a if isinstance(a, NormedRows) else None
-    src = norm.x if norm is not None else a
+    pre = norm.pre if (norm is not None and GEMM_STREAM) else None
+    a_copies = 1
+    if pre is not None:
+        src, norm = pre["xw"][0], None         # the rows times the norm weight; 1/rms is applied to the result rows
+        a_copies = pre["xw"].shape[0]
+    else:
+        src = norm.x if norm is not None else a
+        fan = _fanout.get(src.data_ptr()) if (_fanout and GEMM_STREAM and norm is None) else None
+        if (fan is not None and fan["ref"]() is src and fan["shape"] == tuple(src.shape) and fan["version"] == src._version
+                and src.is_contiguous()):
+            a_copies, src = fan["buf"].shape[0], fan["buf"][0]
     M, K = src.shape
     N = out.shape[1]
     mult = {EPI_SWIGLU: 2, EPI_CONV: 3}.get(epilogue, 1)
@@ -252,12 +321,40 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
         L = taps.shape[1]
         assert taps.shape == (N, L) and state.shape[1:] == (L - 1, N) and taps.dtype == state.dtype == torch.float32
         _i32(slots, "slot_of_row"); _contig(state, "state"); _contig(taps, "taps")
-    lib = load_library("gemm_decode")
-    _check(lib.tuff_gemm_decode(_ptr(src), _ptr(norm.weight if norm is not None else None),
+    if not GEMM_STREAM:
+        _written(out)
+        lib = load_library("gemm_decode")
+        _check(lib.tuff_gemm_decode(_ptr(src), _ptr(norm.weight if norm is not None else None),
+                                    c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
+                                    c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
+                                    c_longlong(out.stride(0)), c_int(epilogue), _ptr(taps), _ptr(state), _ptr(slots),
+                                    c_int(L), c_int(set_block), _stream()), "gemm_decode")
+        return
+    lib = load_library("gemm_stream")
+    st = _tc_buffers(src.device, 0)
+    ann = _norm_announced.pop(out.data_ptr(), None) if (epilogue == EPI_ACCUM and _norm_announced) else None
+    _written(out)
+    emit_w = emit_xw = emit_part = out_fan = None
+    if ann is not None and out.is_contiguous() and tuple(out.shape) == (M, N):
+        emit_w = ann[0]
+        emit_xw = torch.empty((FANOUT, M, N), dtype=torch.bfloat16, device=out.device)
+        emit_part = torch.empty((lib.tuff_gemm_stream_grid(c_int(N)), 16), dtype=torch.float32, device=out.device)
+    if epilogue in (EPI_SWIGLU, EPI_CONV) and FANOUT > 1:
+        out_fan = torch.empty((FANOUT, M, N), dtype=torch.bfloat16, device=out.device)
+    _check(lib.tuff_gemm_stream(_ptr(src), _ptr(norm.weight if norm is not None else None),
                                 c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
                                 c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
                                 c_longlong(out.stride(0)), c_int(epilogue), _ptr(taps), _ptr(state), _ptr(slots),
-                                c_int(L), c_int(set_block), _stream()), "gemm_decode")
+                                c_int(L), c_int(set_block), _ptr(emit_w), _ptr(emit_xw), _ptr(emit_part),
+                                _ptr(pre["part"] if pre is not None else None),
+                                c_int(pre["part"].shape[0] if pre is not None else 0),
+                                c_float(pre["eps"] if pre is not None else 0.0),
+                                c_int(a_copies), c_int(FANOUT), _ptr(out_fan),
+                                _ptr(st["status"]), _stream()), "gemm_stream")
+    if out_fan is not None:
+        _remember(_fanout, out, dict(buf=out_fan, shape=(M, N)))
+    if emit_w is not None:
+        _remember(_norm_ready, out, dict(weight=ann[0], eps=ann[1], xw=emit_xw, part=emit_part, shape=(M, N)))
 
 
 def _decode_eligible(a, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
@@ -329,6 +426,7 @@ def shortconv(bcx: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_o
               row_of_token: torch.Tensor, cu_q: torch.Tensor, out: torch.Tensor, all_single: bool = False) -> None:
     """Gated short convolution of a batch of portions; rolls each row's state slot.
     `all_single`: every row brings exactly one token (one fused launch)."""
+    _written(out)
     n, d = out.shape
     K = taps.shape[1]
     assert bcx.shape == (n, 3 * d) and taps.shape == (d, K) and taps.dtype == torch.float32

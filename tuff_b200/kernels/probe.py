@@ -3,6 +3,7 @@
 
     python -m tuff_b200.kernels.probe gemm_tc --m 2048 --n 11264 --k 2048
     python -m tuff_b200.kernels.probe gemm_decode --m 8 --n 5632 --k 2048 --epilogue swiglu --norm
+    python -m tuff_b200.kernels.probe decode_chain --m 8 --layers 16
     python -m tuff_b200.kernels.probe attention_decode --batch 8 --context 8192
     python -m tuff_b200.kernels.probe attention_prefill --tokens 2048
 
@@ -120,8 +121,10 @@ def run_steps(a) -> int:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_decode", "attention_decode", "attention_prefill",
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_decode", "decode_chain", "attention_decode", "attention_prefill",
                                        "decode_step", "prefill_step", "mixed_step"])
+    ap.add_argument("--layers", type=int, default=16, help="decode_chain: layers of four products each")
+    ap.add_argument("--ffn", type=int, default=5632, help="decode_chain: width of the feed-forward")
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--no-graphs", action="store_true", help="decode_step: plain launches instead of CUDA graph replays")
     ap.add_argument("--m", type=int, default=2048)
@@ -179,6 +182,37 @@ def main(argv=None) -> int:
         nbytes = mult * a.n * a.k * 2
         print(f"gemm_decode m={a.m} n={a.n} k={a.k} {a.epilogue}{' +norm' if a.norm else ''}: {t * 1e6:.1f} us, "
               f"{nbytes / t / 1e9:.0f} GB/s of weights ({nbytes / 1e6:.1f} MB)")
+    elif a.kernel == "decode_chain":
+        # The products of `layers` short-convolution layers back to back, each with weights of its own
+        # (nothing is found in L2 again), replayed from one CUDA graph: what the decode step's products
+        # cost when they follow one another, per product and as bytes over time.
+        d, F, M = a.k, a.ffn, a.m
+        x = torch.randn(M, d, device=dev) * 0.1
+        nw = torch.ones(d, device=dev)
+        layers = []
+        for _ in range(a.layers):
+            layers.append(dict(w_in=(torch.randn(3 * d, d, device=dev) * 0.02).to(bf), w_out=(torch.randn(d, d, device=dev) * 0.02).to(bf),
+                               w13=ops.stack_gate_up((torch.randn(F, d, device=dev) * 0.02).to(bf), (torch.randn(F, d, device=dev) * 0.02).to(bf)), w2=(torch.randn(d, F, device=dev) * 0.02).to(bf),
+                               taps=torch.randn(d, 3, device=dev) * 0.1, state=torch.zeros(M, 2, d, device=dev)))
+        slots = torch.arange(M, dtype=torch.int32, device=dev)
+        g = torch.empty(M, d, dtype=bf, device=dev)
+        act = torch.empty(M, F, dtype=bf, device=dev)
+
+        def chain():
+            for L in layers:
+                ops.gemm_decode(ops.NormedRows(x, nw, 1e-5, bf), L["w_in"], g, ops.EPI_CONV, conv=(L["taps"], L["state"], slots))
+                ops.gemm_decode(g, L["w_out"], x, ops.EPI_ACCUM)
+                ops.gemm_decode(ops.NormedRows(x, nw, 1e-5, bf), L["w13"][0], act, ops.EPI_SWIGLU, set_block=L["w13"][1])
+                ops.gemm_decode(act, L["w2"], x, ops.EPI_ACCUM)
+        chain()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            chain()
+        t = timed(graph.replay, a.reps)
+        nbytes = a.layers * (3 * d * d + d * d + 3 * d * F) * 2
+        print(f"decode_chain m={M} d={d} ffn={F} layers={a.layers}: {t * 1e6:.1f} us for {4 * a.layers} products, "
+              f"{t * 1e6 / (4 * a.layers):.2f} us a product, {nbytes / t / 1e9:.0f} GB/s of weights ({nbytes / 1e6:.0f} MB)")
     else:
         H, G, hd, ps = a.heads, a.kv_heads, a.head_dim, a.page_size
         if a.kernel == "attention_decode":

@@ -2,6 +2,7 @@
 they expect, and the forward pass of one step over the residual stream."""
 from __future__ import annotations
 
+import inspect
 from dataclasses import dataclass
 from typing import Dict, List, Tuple
 
@@ -36,6 +37,8 @@ class Model:
             self._bound += [(bl.block, ls.block), (bl.mixer, ls.mixer), (bl.ffn, ls.ffn),
                             (bl.mixer_norm, ls.mixer_norm), (bl.ffn_norm, ls.ffn_norm)]
         self.schedule: List[ScheduleEntry] = spec.resolved_schedule()
+        # blocks written before `next_norm` existed (or that have no use for it) are called without it
+        self._takes_next_norm = ["next_norm" in inspect.signature(bl.block.forward).parameters for bl in self.layers]
         self.act_dtype: torch.dtype | None = None
         # a position encoding is built inside its mixer; it counts too
         self.replayable = all(getattr(part, "replayable", True) and
@@ -89,7 +92,13 @@ class Model:
     def forward(self, ctx, storages) -> torch.Tensor:
         """Runs the tokens of `ctx` through the schedule; returns fp32 logits [n_wanted, vocab]."""
         x = self.embedding.forward(ctx)
-        for e in self.schedule:
+        for i, e in enumerate(self.schedule):
             layer = self.layers[e.layer]
-            layer.block.forward(ctx, x, layer, storages[e.storage], e.reads_only)
+            if self._takes_next_norm[e.layer]:
+                # the norm that reads the residual after this layer: the next entry's first norm, or the final one
+                nxt = self.layers[self.schedule[i + 1].layer].mixer_norm if i + 1 < len(self.schedule) else (
+                    self.final_norm if ctx.wants_all_rows else None)
+                layer.block.forward(ctx, x, layer, storages[e.storage], e.reads_only, next_norm=nxt)
+            else:
+                layer.block.forward(ctx, x, layer, storages[e.storage], e.reads_only)
         return self.head.forward(ctx, x, self.final_norm)

@@ -18,7 +18,7 @@ Interfaces (ctx is the step's `StepContext`):
   Mixer.forward(ctx, cache, h, residual, reads_only)   residual (fp32 [T, d]) += mixer(h)
   FeedForward.forward(ctx, h, residual)                residual += ffn(h)
   PositionEncoding.rotate(ctx, q, k) or fused_tables() see parts/rope.py
-  Block.forward(ctx, x, layer, cache, reads_only)      runs one layer on the residual x
+  Block.forward(ctx, x, layer, cache, reads_only, next_norm=None)   runs one layer on the residual x
   Embedding.forward(ctx) -> x                          fp32 [T, d]
   Head.forward(ctx, x, norm) -> logits                 fp32 [n_wanted, vocab]
 """
@@ -92,6 +92,10 @@ class Norm(Part):
     def forward(self, ctx, x, row_index=None):
         raise NotImplementedError
 
+    def announce(self, ctx, x) -> None:
+        """Told before the part that writes `x` last runs: this norm will be the next reader of x.
+        A norm may use it to have that write prepare its work; the default does nothing."""
+
 
 class PositionEncoding(Part):
     pass
@@ -111,7 +115,9 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    def forward(self, ctx, x, layer, cache, reads_only: bool = False) -> None:
+    def forward(self, ctx, x, layer, cache, reads_only: bool = False, next_norm=None) -> None:
+        """`next_norm`: the norm that reads x after this layer (the next layer's first norm, or the
+        final norm), if the caller knows it; a block may `announce` x to it before its last write."""
         raise NotImplementedError
 
 

@@ -17,6 +17,11 @@ class RMSNorm(Norm):
     def weight_decls(self):
         return {"weight": WeightDecl((self.dim,), role="vector", init="norm")}
 
+    def announce(self, ctx, x):
+        # few rows in bf16: the decode product that adds into x last can prepare this norm
+        if x.shape[0] <= ops.SKINNY_MAX_TOKENS and self.act_dtype == torch.bfloat16:
+            ops.announce_norm(x, self.w["weight"], self.eps)
+
     def forward(self, ctx, x, row_index=None, lazy=False):
         """`lazy`: the caller's next step is a matrix product that can norm its own rows; it gets
         an `ops.NormedRows` (which any other consumer turns into the tensor with `.dense()`)."""
