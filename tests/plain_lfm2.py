@@ -174,9 +174,10 @@ class PlainLfm2:
         self.kinds = layer_kinds(cfg)
         self.tied = cfg.get("tie_embedding", True)
 
-    def forward(self, tokens):
+    def forward(self, tokens, rows=None):
         """Logits [T, vocab] (float64) for a whole sequence; layer order and residuals
-        as in src/lfm25_engine.c:365-423."""
+        as in src/lfm25_engine.c:365-423.  `rows`: positions whose logits are wanted (all if None);
+        the sequence runs whole either way."""
         w = self.w
         x = embed(w["model.embed_tokens.weight"], tokens)
         for i, kind in enumerate(self.kinds):
@@ -196,6 +197,8 @@ class PlainLfm2:
             f = p + "feed_forward."
             x = x + swiglu_ffn(h, w[f + "w1.weight"], w[f + "w3.weight"], w[f + "w2.weight"])
         out_w = w["model.embed_tokens.weight"] if self.tied else w["lm_head.weight"]
+        if rows is not None:
+            x = x[np.asarray(rows)]
         return lm_head(x, w["model.embedding_norm.weight"], self.eps, out_w)
 
 

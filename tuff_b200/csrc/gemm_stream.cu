@@ -50,7 +50,6 @@ constexpr int NORM_BLOCKS = 2;               // the fused RMSNorm holds rows of 
 constexpr int MAX_ROWS = 64;                 // weight rows (all sets) of one pass
 constexpr int BK = 64;                       // K elements of one tile: 128 bytes, one swizzle row
 constexpr int PART_STRIDE = 16;              // floats per CTA in the buffer of partial sums of squares
-#define K_BYTES(k) ((k) * 2)
 constexpr int MAX_TAPS = 4;                  // taps of the convolution whose state is fetched ahead
 
 enum : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_CONV = 3 };
@@ -58,9 +57,6 @@ enum : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_CONV = 3 };
 struct StreamGemm {
     const void* a;            // NORM: fp32 residual [M, K] (lda); else unused (the activations come by TMA)
     const float* norm_w;      // RMSNorm weight [K]
-    const bf16* w;            // [sets * N, K] (ldw): for the prefetch into L2; the loads go through the tensor map
-    long long ldw;
-    int prefetch_lines;       // how many 128-byte lines of its share of W a CTA asks into L2 when it starts
     void* out;                // [M, ldc]
     int* status;
     long long lda, ldc;
@@ -87,9 +83,6 @@ struct StreamGemm {
     int a_bytes;              // bytes of the activation region (whole normed rows, or a ring beside the weights')
     int red_stride;           // floats per (warp, token) row of the reduction buffer
     int k_inner;              // 1: K is not a multiple of 64; stages are single K blocks cut from a [rows, K] view
-    int a_copies;             // A lies in memory this many times ([copies][M][K]); a CTA reads copy blockIdx.x % a_copies
-    int out_copies;           // copies of a bf16 result written to out_fan ([copies][M][N]) beside `out`; emit_xw has as many
-    bf16* out_fan;
     int a_kb;                 // a_resident: K blocks of a row in shared memory (n_kb rounded up to odd)
     int a_resident;           // 1: the bf16 activations are loaded once, whole, and stay for all passes (else a ring beside the weights')
     long long* trace;         // null, or 8 time stamps per CTA of this launch (tuff_gemm_stream_trace)
@@ -205,7 +198,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // activations beside them (only after griddepcontrol.wait).  One load per stage each: all sets, all
     // rows, kb_per_stage K blocks (blocks past the end of K are filled with zeros).
     StageCursor w_cur(p, spp), a_cur(p, spp);
-    const int a_copy = p.a_copies > 1 ? (int)(blockIdx.x % p.a_copies) : 0;
     uint32_t n_w = 0, n_a = 0, w_phase = 1;        // w_phase: parity of the empty barrier's phase that frees the next slot
     int w_slot = 0, a_slot = 0;
     auto issue_w = [&]() {
@@ -218,7 +210,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     };
     auto issue_a = [&]() {
         const int s = a_slot, kb0 = a_cur.st * jb;
-        tma_load_5d(a_region + (uint32_t)(s * a_stage), &map_a, full_bar(s), p.k_inner ? kb0 * BK : 0, p.k_inner ? 0 : kb0, 0, 0, a_copy);
+        tma_load_5d(a_region + (uint32_t)(s * a_stage), &map_a, full_bar(s), p.k_inner ? kb0 * BK : 0, p.k_inner ? 0 : kb0, 0, 0, 0);
         a_cur.next(); ++n_a;
         if (++a_slot == S) a_slot = 0;
     };
@@ -228,33 +220,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         while ((int)n_w < S && w_cur.valid()) issue_w();
     }
     __syncwarp();
-    // The rest of this CTA's share of W (what the ring does not hold yet) is asked into L2 now, by all
-    // threads, a line each: while the kernel before this one computes, HBM brings this kernel's
-    // weights, and the ring's later loads find them in L2.  So the ring has to cover the latency of
-    // L2, not of HBM, and can be small enough for two kernels' CTAs to share an SM.  The prefetches
-    // hold nothing in the SM while they are under way.
-    if (p.prefetch_lines > 0) {
-        const int lines_per_row = (K_BYTES(p.K) + 127) >> 7;
-        int budget = p.prefetch_lines;
-        for (StageCursor pc(p, 1); pc.valid() && budget > 0; pc.next_pass()) {
-            const int n = pc.width(), blk = pc.c / p.set_block, ci = pc.c - blk * p.set_block;
-            const int total = p.sets * n * lines_per_row;
-            for (int i = threadIdx.x; i < min(total, budget); i += THREADS) {
-                const int row = i / lines_per_row, line = i - row * lines_per_row;
-                const int set = row / n, r = row - set * n;
-                const char* a = reinterpret_cast<const char*>(p.w + ((size_t)(blk * p.sets + set) * p.set_block + ci + r) * p.ldw) + (size_t)line * 128;
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-            }
-            budget -= total;
-        }
-    }
     pdl_wait();
     if (trace && threadIdx.x == 0) trace[1] = global_ns();
     if (producer && !NORM) {
         if (p.a_resident) {
             // all of A in one load: it stays for every pass (a_kb blocks a row, an odd number: see swz)
             mbar_expect_tx(a_full, (uint32_t)(p.a_kb * A_TILE));
-            tma_load_5d(a_region, &map_a, a_full, 0, 0, 0, 0, a_copy);
+            tma_load_5d(a_region, &map_a, a_full, 0, 0, 0, 0, 0);
         } else {
             while (n_a < n_w) issue_a();
         }
@@ -503,15 +475,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 v[e] = a * scale;
             }
             const size_t o = (size_t)tok * p.ldc + col;
-            // a bf16 result that another product of this kind reads as its activations is written several
-            // times, and every CTA of that product reads one of the copies: 148 CTAs that ask for the same
-            // few lines at once wait for one another in L2
-            auto store_bf16 = [&](float val) {
-                const bf16 b = __float2bfloat16_rn(val);
-                reinterpret_cast<bf16*>(p.out)[o] = b;
-                if (p.out_fan)
-                    for (int cp = 0; cp < p.out_copies; ++cp) p.out_fan[((size_t)cp * p.M + tok) * p.N + col] = b;
-            };
+            auto store_bf16 = [&](float val) { reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val); };
             if (p.epi == EPI_STORE) {
                 if (p.out_dtype == TUFF_F32) reinterpret_cast<float*>(p.out)[o] = v[0];
                 else store_bf16(v[0]);
@@ -520,8 +484,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const float x_new = (fetched ? pre_res : ld_act(op)) + v[0];
                 *op = x_new;
                 if (p.emit_w) {
-                    const bf16 b = __float2bfloat16_rn(x_new * (fetched ? pre_emit_w : p.emit_w[col]));
-                    for (int cp = 0; cp < p.out_copies; ++cp) p.emit_xw[((size_t)cp * p.M + tok) * p.N + col] = b;
+                    p.emit_xw[(size_t)tok * p.N + col] = __float2bfloat16_rn(x_new * (fetched ? pre_emit_w : p.emit_w[col]));
                     sq[tok * pc + c] = x_new * x_new;
                 }
             } else if (p.epi == EPI_SWIGLU) {
@@ -639,19 +602,6 @@ int smem_target() {
     return v;
 }
 
-int prefetch_kb() {
-    // How much of its share of W a CTA asks into L2 at its start, in KB (TUFF_STREAM_PREFETCH overrides it
-    // for sweeps; 0 switches the prefetch off): 384 KB a CTA is 57 MB over 148 CTAs, under half of L2.
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("TUFF_STREAM_PREFETCH");
-        v = e ? atoi(e) : 384;
-        if (v < 0) v = 0;
-        if (v > 2048) v = 2048;
-    }
-    return v;
-}
-
 int stream_grid(int N) { return std::min(sm_count(), ceil_div(N, 8)); }
 
 template <int MT, bool NORM, int NGT>
@@ -688,15 +638,11 @@ extern "C" int tuff_gemm_stream_grid(int N) { return N > 0 ? stream_grid(N) : 0;
 // sum of squares of the CTA's columns of C.  scale_part (A bf16 only; else null): such a buffer
 // with scale_parts rows for the rows of A; every result row r is multiplied by
 // rsqrt(sum over CTAs of scale_part[.][r] / K + scale_eps) before the epilogue.
-// a_copies: A (bf16, lda == K) lies in memory that many times, M * lda elements apart, and each CTA reads
-// one copy.  out_copies: emit_xw is [out_copies, M, N], and so is out_fan, which (if not null) receives
-// copies of a bf16 C.
 extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, const void* W, void* C, int c_dtype,
                                 int M, int N, int K, long long lda, long long ldw, long long ldc, int epilogue,
                                 const float* taps, float* state, const int* slot_of_row, int L, int set_block,
                                 const float* emit_w, void* emit_xw, float* emit_part,
                                 const float* scale_part, int scale_parts, float scale_eps,
-                                int a_copies, int out_copies, void* out_fan,
                                 int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || epilogue < 0 || epilogue > 3 || !status) return TUFF_E_SIZE;
@@ -710,18 +656,16 @@ extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, c
     if (set_block < 0 || (set_block && N % set_block)) return TUFF_E_SIZE;
     if (emit_w && (epilogue != EPI_ACCUM || !emit_xw || !emit_part)) return TUFF_E_SIZE;
     if (scale_part && (norm_w || scale_parts <= 0 || scale_parts > 256)) return TUFF_E_SIZE;
-    if (a_copies < 1 || out_copies < 1 || (norm_w && a_copies > 1) || (out_fan && c_dtype != TUFF_BF16)) return TUFF_E_SIZE;
     const bool norm = norm_w != nullptr;
     const int MT = M <= 8 ? 8 : 16;
     StreamGemm p{};
-    p.a = A; p.norm_w = norm_w; p.w = (const bf16*)W; p.ldw = ldw; p.out = C; p.status = status; p.lda = lda; p.ldc = ldc;
+    p.a = A; p.norm_w = norm_w; p.out = C; p.status = status; p.lda = lda; p.ldc = ldc;
     p.M = M; p.N = N; p.K = K; p.eps = eps; p.epi = epilogue; p.out_dtype = c_dtype;
     p.sets = epilogue == EPI_SWIGLU ? 2 : epilogue == EPI_CONV ? 3 : 1;
     p.set_block = (set_block && p.sets > 1) ? set_block : N;
     p.taps = taps; p.state = state; p.slot_of_row = slot_of_row; p.L = L;
     p.emit_w = emit_w; p.emit_xw = (bf16*)emit_xw; p.emit_part = emit_part;
     p.scale_part = scale_part; p.scale_parts = scale_parts; p.scale_eps = scale_eps;
-    p.a_copies = a_copies; p.out_copies = out_copies; p.out_fan = (bf16*)out_fan;
     // every SM an equal share of the columns, in passes of at most MAX_ROWS weight rows
     const int grid = stream_grid(N);
     const int nblk = N / p.set_block;
@@ -760,12 +704,11 @@ extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, c
     p.a_bytes = (norm || p.a_resident) ? a_whole : S * p.kb_per_stage * a_tile;
     const size_t smem = (size_t)fixed + (size_t)S * stage_bytes;
     if (smem > 227 * 1024) return TUFF_E_SIZE;
-    p.prefetch_lines = prefetch_kb() * 8;
     if (g_trace && g_trace_launches < g_trace_capacity && grid <= 256) p.trace = g_trace + (size_t)(g_trace_launches++) * 256 * 8;
     CUtensorMap mw, ma;
     if (!stream_map(&mw, W, K, p.set_block, p.sets, N / p.set_block, ldw, p.kb_per_stage, p.pass_cols, p.sets)) return TUFF_E_ALIGN;
     if (norm) ma = mw;                                            // not used
-    else if (!stream_map(&ma, A, K, M, 1, a_copies, lda, p.a_resident ? p.a_kb : p.kb_per_stage, MT, 1)) return TUFF_E_ALIGN;
+    else if (!stream_map(&ma, A, K, M, 1, 1, lda, p.a_resident ? p.a_kb : p.kb_per_stage, MT, 1)) return TUFF_E_ALIGN;
     const int ngt = p.tile_rows / 16;
 #define TUFF_PICK(NGV)                                                                                         \
     (MT == 8 ? (norm ? launch<8, true, NGV>(mw, ma, p, grid, smem, stream) : launch<8, false, NGV>(mw, ma, p, grid, smem, stream)) \

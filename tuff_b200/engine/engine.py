@@ -14,6 +14,7 @@ from typing import Dict, List, Sequence
 
 import torch
 
+from ..kernels import ops
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, SampleRow
 from .batch import StepEntry
@@ -79,11 +80,27 @@ class Engine:
             nxt_plan = self.scheduler.plan_ahead(plan)
             if nxt_plan is not None:
                 nxt = (nxt_plan, self._launch(nxt_plan, sampled_dev))
-        sampled = sampled_dev.tolist() if sampled_dev is not None else []
+        sampled = self._read_ids(sampled_dev) if sampled_dev is not None else []
         finished = self.scheduler.update(plan, sampled)
         if nxt is not None and self.scheduler.running:
             self._ahead = nxt
         return finished
+
+    def _read_ids(self, sampled_dev: torch.Tensor) -> List[int]:
+        """The sampled ids on the host, read together with the kernels' status word (one copy, one wait):
+        a kernel whose bounded wait ran out has left a code there, and what the step wrote is invalid."""
+        both = torch.cat([sampled_dev.view(-1), ops.status_word(self.runner.device)]).tolist()
+        if both[-1]:
+            self.reset()
+            ops.raise_on_status(both[-1])
+        return both[:-1]
+
+    def reset(self) -> None:
+        """Aborts every request (their pages and slots are free again) and forgets a step that was
+        launched ahead; the engine is then as it was before the first request."""
+        self._ahead = None
+        for req in list(self.scheduler.running) + list(self.scheduler.waiting):
+            self.scheduler.abort(req)
 
     @staticmethod
     def _may_run_ahead(plan: StepPlan) -> bool:

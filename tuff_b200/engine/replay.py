@@ -20,6 +20,7 @@ import sys
 from typing import Dict, IO
 
 from ..cache.manager import RequestCache
+from ..kernels import ops
 from .batch import StepEntry
 from .runner import ModelRunner
 
@@ -53,6 +54,7 @@ def replay(runner: ModelRunner, lines: IO[str], out_dir: str, report: IO[str] = 
             logits = runner.step(entries)
             if logits.shape[0] > 0:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+                ops.check_tc_status()          # the copy has waited for the step: a wait that ran out shows here
                 tmp = os.path.join(out_dir, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))

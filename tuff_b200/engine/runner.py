@@ -71,6 +71,8 @@ class ModelRunner:
         self.max_context = min(x for x in (max_context, limit, 1 << 30) if x is not None)
         self.cache = CacheManager(self.model.storage_needs(), page_size, max_tokens, max_requests,
                                   dtype=self.dtype, device=self.device)
+        # scratch memory of the kernels at its final size and address before any step can be captured
+        self.model.reserve(self.device, max_requests, self.max_context)
 
     # ---- requests ------------------------------------------------------------
     def open(self, request_id) -> RequestCache:

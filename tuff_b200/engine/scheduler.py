@@ -87,6 +87,7 @@ class PlannedEntry:
     request: Request
     tokens: List[int]
     samples: bool                          # the portion ends the known tokens: its last logits pick the next one
+    start: int = 0                         # position of the portion's first token, as planned
 
 
 @dataclass
@@ -210,7 +211,7 @@ class Scheduler:
             if req.status is not RequestStatus.RUNNING or not self._fits(need, free):
                 continue
             self._take(need, free)
-            plan.entries.append(PlannedEntry(req, req.token_slice(req.n_cached), True))
+            plan.entries.append(PlannedEntry(req, req.token_slice(req.n_cached), True, req.n_cached))
             planned.add(id(req))
             budget -= 1
         # 2. portions of running prompts
@@ -222,7 +223,7 @@ class Scheduler:
                 continue
             self._take(self.cache.pages_needed(req.cache, n), free)
             toks = req.token_slice(req.n_cached, req.n_cached + n)
-            plan.entries.append(PlannedEntry(req, toks, n == req.n_pending()))
+            plan.entries.append(PlannedEntry(req, toks, n == req.n_pending(), req.n_cached))
             planned.add(id(req))
             budget -= n
         # 3. admission (not in a step that had to preempt: the freed pages are for those who run)
@@ -238,7 +239,7 @@ class Scheduler:
             plan.admitted.append(req)
             self.stats["admitted"] += 1
             self._take(self.cache.pages_needed(req.cache, n), free)
-            plan.entries.append(PlannedEntry(req, req.token_slice(0, n), n == req.n_pending()))
+            plan.entries.append(PlannedEntry(req, req.token_slice(0, n), n == req.n_pending(), 0))
             planned.add(id(req))
             budget -= n
 
@@ -268,7 +269,7 @@ class Scheduler:
             if not self._fits(need, free):
                 return None
             self._take(need, free)
-            plan.entries.append(PlannedEntry(req, [0], True))
+            plan.entries.append(PlannedEntry(req, [0], True, req.n_cached))
         self.stats["steps"] += 1
         return plan
 
@@ -293,8 +294,8 @@ class Scheduler:
                 if e.samples:
                     next(it)
                 continue
-            start = req.n_cached - len(e.tokens)            # the step has run: the cache counts its tokens
-            self.stats["prompt_tokens"] += max(0, min(len(req.prompt), req.n_cached) - start)
+            # counted from the position planned for the portion (the cache may already count a step launched after this one)
+            self.stats["prompt_tokens"] += max(0, min(len(req.prompt), e.start + len(e.tokens)) - e.start)
             if not e.samples:
                 continue
             tok = int(next(it))

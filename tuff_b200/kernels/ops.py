@@ -150,23 +150,36 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: 
 _tc_state: dict = {}
 
 
+def _grow(st: dict, n_floats: int, what: str) -> None:
+    """Makes st["ws"] hold at least n_floats.  A workspace that is replaced stays alive (st["retired"]):
+    a CUDA graph captured earlier has its address in its kernels' arguments and goes on writing
+    there when it is replayed.  Sizes at least double, so all retired ones together stay smaller
+    than the current one."""
+    if st["ws"] is not None and st["ws"].numel() >= n_floats:
+        return
+    if torch.cuda.is_current_stream_capturing():
+        raise KernelError(f"the {what} workspace would have to grow inside a CUDA graph capture; "
+                          "run the step once before capturing it, or reserve it (ops.reserve_workspaces)")
+    if st["ws"] is not None:
+        st.setdefault("retired", []).append(st["ws"])
+        n_floats = max(n_floats, 2 * st["ws"].numel())
+    st["ws"] = torch.empty(n_floats, dtype=torch.float32, device=st["device"])
+
+
 def _tc_buffers(device: torch.device, need_bytes: int):
     """The tensor-core product's device status word and split-K workspace (grown on demand)."""
     st = _tc_state.get(device)
     if st is None:
-        st = _tc_state[device] = {"status": torch.zeros(1, dtype=torch.int32, device=device), "ws": None}
-    if need_bytes and (st["ws"] is None or st["ws"].numel() * 4 < need_bytes):
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("the split-K workspace would have to grow inside a CUDA graph capture; "
-                              "run the step once before capturing it")
-        st["ws"] = torch.empty((need_bytes + 3) // 4, dtype=torch.float32, device=device)
+        st = _tc_state[device] = {"status": torch.zeros(1, dtype=torch.int32, device=device), "ws": None, "device": device}
+    if need_bytes:
+        _grow(st, (need_bytes + 3) // 4, "split-K")
     return st
 
 
 def tc_status(device=None) -> int:
     """The status word of the tensor-core kernels (synchronises); non-zero means a bounded wait
-    ran out: in the tensor-core product 1 producer, 2 MMA issuer, 3 epilogue, 4 accumulator hand-back
-    (51-54 the same by pairs of CTAs); in attention 11/12 decode producer/consumer, 21/22 prompt
+    ran out: in the tensor-core product 1 producer, 2 MMA issuer, 3 epilogue, 4 accumulator hand-back;
+    in the decode product 61 producer, 63 consumers; in attention 11/12 decode producer/consumer, 21/22 prompt
     portions on mma.sync producer/consumer; in the tcgen05 attention 31 producer, 32-36 MMA issuer
     (query, keys, score buffer, P, -), 37-41 softmax warps (scores, last tile's values, O before a
     rescale, P buffer, final O)."""
@@ -178,9 +191,19 @@ def tc_status(device=None) -> int:
 
 
 def check_tc_status() -> None:
-    code = tc_status()
+    raise_on_status(tc_status())
+
+
+def raise_on_status(code: int) -> None:
     if code:
-        raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}); its results are invalid")
+        raise KernelError(f"a kernel gave up waiting on a barrier (code {code}, see ops.tc_status); "
+                          "the results of the step are invalid")
+
+
+def status_word(device) -> torch.Tensor:
+    """The device int32 in which a kernel whose bounded wait ran out leaves its code (0: all is well).
+    Read it together with a step's results, at the point where the host waits for them anyway."""
+    return _tc_buffers(torch.device(device), 0)["status"]
 
 
 def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
@@ -226,27 +249,21 @@ FUSED_NORM_MAX_K = 2048          # the widest row the fused RMSNorm of a decode 
 # operation changes x._version).
 _norm_announced: dict = {}
 _norm_ready: dict = {}
-# What a decode product writes for another decode product to read as its activations, it writes
-# FANOUT times ([FANOUT, M, N]), and each CTA of the reader takes one copy: all CTAs need all of it
-# at the same moment, and 148 requests for the same few lines wait for one another in L2.
-FANOUT = max(1, int(os.environ.get("TUFF_STREAM_COPIES", "8")))
-_fanout: dict = {}
 
 
 def announce_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
     """The next decode product that adds into `x` (fp32 [M, d], M <= 16) may prepare RMSNorm(x; weight, eps)."""
-    if (GEMM_STREAM and x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= SKINNY_MAX_TOKENS
+    if (x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= SKINNY_MAX_TOKENS
             and x.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == x.shape[1]):
         _norm_announced[x.data_ptr()] = (weight, float(eps))
 
 
 def _written(t: torch.Tensor) -> None:
     """`t` is about to be written by a kernel of this module: what was prepared from its old values is void."""
-    if _norm_announced or _norm_ready or _fanout:
+    if _norm_announced or _norm_ready:
         ptr = t.data_ptr()
         _norm_announced.pop(ptr, None)
         _norm_ready.pop(ptr, None)
-        _fanout.pop(ptr, None)
 
 
 def _remember(table: dict, t: torch.Tensor, rec: dict) -> None:
@@ -291,25 +308,18 @@ class NormedRows:
 
 
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_CONV = 0, 1, 2, 3
-GEMM_STREAM = os.environ.get("TUFF_GEMM_STREAM", "1") != "0"
 
 
 def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, conv=None, set_block: int = 0) -> None:
-    """A decode-step product for at most 16 tokens with its neighbours fused in (csrc/gemm_decode.cu):
+    """A decode-step product for at most 16 tokens with its neighbours fused in (csrc/gemm_stream.cu):
     `a` is a bf16 tensor [M, K] or a `NormedRows`; epilogue EPI_SWIGLU takes w = [gate; up] stacked,
     EPI_CONV takes w = [B; C; x] stacked and conv = (taps [d, L], state [slots, L-1, d], slot_of_row)."""
     norm = a if isinstance(a, NormedRows) else None
-    pre = norm.pre if (norm is not None and GEMM_STREAM) else None
-    a_copies = 1
+    pre = norm.pre if norm is not None else None
     if pre is not None:
-        src, norm = pre["xw"][0], None         # the rows times the norm weight; 1/rms is applied to the result rows
-        a_copies = pre["xw"].shape[0]
+        src, norm = pre["xw"], None            # the rows times the norm weight; 1/rms is applied to the result rows
     else:
         src = norm.x if norm is not None else a
-        fan = _fanout.get(src.data_ptr()) if (_fanout and GEMM_STREAM and norm is None) else None
-        if (fan is not None and fan["ref"]() is src and fan["shape"] == tuple(src.shape) and fan["version"] == src._version
-                and src.is_contiguous()):
-            a_copies, src = fan["buf"].shape[0], fan["buf"][0]
     M, K = src.shape
     N = out.shape[1]
     mult = {EPI_SWIGLU: 2, EPI_CONV: 3}.get(epilogue, 1)
@@ -321,26 +331,15 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
         L = taps.shape[1]
         assert taps.shape == (N, L) and state.shape[1:] == (L - 1, N) and taps.dtype == state.dtype == torch.float32
         _i32(slots, "slot_of_row"); _contig(state, "state"); _contig(taps, "taps")
-    if not GEMM_STREAM:
-        _written(out)
-        lib = load_library("gemm_decode")
-        _check(lib.tuff_gemm_decode(_ptr(src), _ptr(norm.weight if norm is not None else None),
-                                    c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
-                                    c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
-                                    c_longlong(out.stride(0)), c_int(epilogue), _ptr(taps), _ptr(state), _ptr(slots),
-                                    c_int(L), c_int(set_block), _stream()), "gemm_decode")
-        return
     lib = load_library("gemm_stream")
     st = _tc_buffers(src.device, 0)
     ann = _norm_announced.pop(out.data_ptr(), None) if (epilogue == EPI_ACCUM and _norm_announced) else None
     _written(out)
-    emit_w = emit_xw = emit_part = out_fan = None
+    emit_w = emit_xw = emit_part = None
     if ann is not None and out.is_contiguous() and tuple(out.shape) == (M, N):
         emit_w = ann[0]
-        emit_xw = torch.empty((FANOUT, M, N), dtype=torch.bfloat16, device=out.device)
+        emit_xw = torch.empty((M, N), dtype=torch.bfloat16, device=out.device)
         emit_part = torch.empty((lib.tuff_gemm_stream_grid(c_int(N)), 16), dtype=torch.float32, device=out.device)
-    if epilogue in (EPI_SWIGLU, EPI_CONV) and FANOUT > 1:
-        out_fan = torch.empty((FANOUT, M, N), dtype=torch.bfloat16, device=out.device)
     _check(lib.tuff_gemm_stream(_ptr(src), _ptr(norm.weight if norm is not None else None),
                                 c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
                                 c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
@@ -349,10 +348,7 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
                                 _ptr(pre["part"] if pre is not None else None),
                                 c_int(pre["part"].shape[0] if pre is not None else 0),
                                 c_float(pre["eps"] if pre is not None else 0.0),
-                                c_int(a_copies), c_int(FANOUT), _ptr(out_fan),
                                 _ptr(st["status"]), _stream()), "gemm_stream")
-    if out_fan is not None:
-        _remember(_fanout, out, dict(buf=out_fan, shape=(M, N)))
     if emit_w is not None:
         _remember(_norm_ready, out, dict(weight=ann[0], eps=ann[1], xw=emit_xw, part=emit_part, shape=(M, N)))
 
@@ -497,13 +493,36 @@ _attn_state: dict = {}
 
 
 def _attn_workspace(device: torch.device, n_floats: int) -> torch.Tensor | None:
-    st = _attn_state.setdefault(device, {"ws": None})
-    if n_floats and (st["ws"] is None or st["ws"].numel() < n_floats):
-        if torch.cuda.is_current_stream_capturing():
-            raise KernelError("the attention workspace would have to grow inside a CUDA graph capture; "
-                              "run the step once before capturing it")
-        st["ws"] = torch.empty(n_floats, dtype=torch.float32, device=device)
+    st = _attn_state.setdefault(device, {"ws": None, "device": device})
+    if n_floats:
+        _grow(st, n_floats, "attention")
     return st["ws"] if n_floats else None
+
+
+def reserve_attention_workspace(device, max_rows: int, max_context: int, heads: int, kv_heads: int, head_dim: int) -> None:
+    """Sizes the sliced decode attention's workspace once for up to `max_rows` one-token rows at contexts
+    up to `max_context`, so that it keeps one address (a CUDA graph captured with it may be replayed
+    after steps with other row counts have run)."""
+    device = torch.device(device)
+    with torch.cuda.device(device):
+        lib = load_library("attention_flash")
+        if not lib.tuff_attention_flash_supported(c_int(heads), c_int(kv_heads), c_int(head_dim), c_int(64)):
+            return
+        lib.tuff_attention_decode_workspace_floats.restype = c_longlong
+        need = 0
+        for n in range(1, max(1, max_rows) + 1):
+            splits = lib.tuff_attention_decode_splits(c_int(n), c_int(kv_heads), c_int(max(1, max_context)))
+            need = max(need, lib.tuff_attention_decode_workspace_floats(c_int(n), c_int(heads), c_int(head_dim), c_int(splits)))
+        _attn_workspace(device, int(need))
+
+
+def reserve_product_workspace(device, widest_out: int, widest_in: int) -> None:
+    """The same for the partial sums of the tensor-core product with few tokens (17..128)."""
+    device = torch.device(device)
+    with torch.cuda.device(device):
+        lib = load_library("gemm_tc")
+        lib.tuff_gemm_tc_workspace_bytes.restype = c_longlong
+        _tc_buffers(device, int(lib.tuff_gemm_tc_workspace_bytes(c_int(128), c_int(max(1, widest_out)), c_int(max(8, widest_in)))))
 
 
 def attention_flash_supported(q: torch.Tensor, k_pages: torch.Tensor, H: int, G: int, hd: int) -> bool:

@@ -66,6 +66,17 @@ class Model:
             local = {l: tensors[ps.tensors[l]] for l in part.weight_decls()}
             part.bind(local, act_dtype)
 
+    def reserve(self, device, max_rows: int, max_context: int) -> None:
+        """Lets every part size its scratch memory, and the products theirs for the widest matrix."""
+        for part, _ in self._bound:
+            part.reserve(device, max_rows, max_context)
+        if self.act_dtype == torch.bfloat16:
+            from ..kernels import ops
+            mats = [d.shape for d in self.expected_tensors().values() if d.role == "matrix" and len(d.shape) == 2]
+            if mats:
+                # stacked matrices (q|k|v, gate|up, B|C|x) are up to three times as tall as a declared one
+                ops.reserve_product_workspace(device, 3 * max(m[0] for m in mats), max(m[1] for m in mats))
+
     # ---- cache -------------------------------------------------------------
     def storage_needs(self) -> List[object]:
         """What each cache storage must hold, indexed by storage number (None: nothing)."""

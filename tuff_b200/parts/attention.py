@@ -45,6 +45,10 @@ class GQAAttention(Mixer):
             decls["k_layernorm"] = WeightDecl((hd,), role="vector", init="norm")
         return decls
 
+    def reserve(self, device, max_rows, max_context):
+        if self.act_dtype == torch.bfloat16:
+            ops.reserve_attention_workspace(device, max_rows, max_context, self.H, self.G, self.hd)
+
     def cache_need(self):
         return PagedKVNeed(kv_heads=self.G, head_dim=self.hd, window=self.window)
 

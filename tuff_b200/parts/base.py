@@ -79,6 +79,10 @@ class Part:
     # plain launches.
     replayable: bool = True
 
+    def reserve(self, device, max_rows: int, max_context: int) -> None:
+        """Called once before the first step: a part whose kernels use scratch memory sizes it here for
+        the most rows a step may bring and the longest context, so that it never moves afterwards."""
+
     def weight_decls(self) -> Dict[str, WeightDecl]:
         return {}
 
