@@ -14,8 +14,9 @@ which yields one logits row per position).  The reference script fixes the
 convolution at 3 taps and the head size at hidden/heads, so both cases have
 conv_L_cache = 3; sizes with 4 taps rest on the formulas alone.
 
-Stored per case: the configuration, the weight seed, a checksum of the weights,
-the tokens, and the logits as float32 [T, vocab].
+Stored per case: the configuration, the weight seed, the model.safetensors file
+itself (the test needs no random generator to have the same weights), a checksum
+of the weights, the tokens, and the logits as float32 [T, vocab].
 """
 import hashlib
 import json
@@ -117,6 +118,8 @@ def main():
             out[name + ".config"] = np.frombuffer(json.dumps(cfg).encode(), dtype=np.uint8)
             out[name + ".seed"] = np.int64(case["seed"])
             out[name + ".checksum"] = np.frombuffer(weights_checksum(w).encode(), dtype=np.uint8)
+            with open(os.path.join(folder, "model.safetensors"), "rb") as f:
+                out[name + ".safetensors"] = np.frombuffer(f.read(), dtype=np.uint8)      # the weights themselves
             out[name + ".tokens"] = np.asarray(toks, np.int32)
             out[name + ".logits"] = logits
             print(name, logits.shape, float(np.abs(logits).max()))

@@ -46,6 +46,7 @@ def run_trace(folder, dtype, steps, tmp_path, page_size=16, max_tokens=None):
     from tuff_b200.engine.runner import ModelRunner
     n = max_tokens or traces.tokens_needed(steps)
     runner = ModelRunner(folder, dtype=dtype, max_tokens=n, page_size=page_size, max_requests=4)
+    runner.cache.owners = {}                      # log every hand-out of a page
     text = "\n".join(json.dumps(s) for s in steps) + "\n"
     log = io.StringIO()
     replay(runner, io.StringIO(text), str(tmp_path), report=log)
@@ -80,9 +81,43 @@ def test_replay_modes(models, tmp_path, name, dtype, mode):
     runner = run_trace(folder, dtype, steps, tmp_path, page_size=page)
     compare(str(tmp_path), wanted, expect, vocab, dtype, f"{name} {mode}")
     if mode == "mixed":
-        # the pool is smaller than what all requests together need, so pages were used again
-        total = sum((len(t) + 63) // 64 * 64 for t in reqs.values())
-        assert runner.cache.num_pages * runner.cache.page_size < total
+        # pages were used again: the pool's own log shows pages that two different requests held
+        reused = [k for k, who in runner.cache.owners.items() if len(set(who)) > 1]
+        assert len(reused) >= 2, runner.cache.owners
+
+
+def logits_by_place(out_dir, wanted, vocab):
+    out = {}
+    for step, rows in wanted.items():
+        got = np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4").reshape(len(rows), vocab)
+        for i, place in enumerate(rows):
+            out[place] = got[i].copy()
+    return out
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_float32_logits_are_bitwise_equal_in_every_mode(models, tmp_path, name):
+    """The 32-bit path adds in an order that depends on sizes only: the logits of a (request, position)
+    are the same bits whether the request ran whole, with its tail decoded, in portions, or mixed with
+    others in reused pages (the reference's gate: tests/verify_lfm25_prefill.sh:28-54 compares its batched
+    and its one-by-one prefill with `cmp`, tests/verify_lfm25_golden.sh:247-272 hashes every logits row
+    under every execution mode)."""
+    folder, reqs, _ = models[name]
+    vocab = CONFIGS[name][0]["vocab_size"]
+    page = {"tiny_a": 16, "tiny_b": 4, "tiny_c": 8, "tiny_d": 8}[name]
+    seen = {}
+    for mode in ("whole", "tail_decoded", "portions", "mixed"):
+        steps, wanted = getattr(traces, mode)(reqs)
+        out = tmp_path / mode
+        run_trace(folder, "float32", steps, out, page_size=page)
+        for place, row in logits_by_place(str(out), wanted, vocab).items():
+            if place in seen:
+                same = np.array_equal(seen[place][1].view(np.uint32), row.view(np.uint32))
+                assert same, (f"{name}: request {place[0]} position {place[1]} differs between {seen[place][0]} and {mode}: "
+                              f"max difference {np.abs(seen[place][1] - row).max():.3g}")
+            else:
+                seen[place] = (mode, row)
+    assert len(seen) == sum(len(t) for t in reqs.values())
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -94,6 +94,9 @@ class CacheManager:
         self.slots = UnitPool(self.max_requests, "slot")
         self.has_state = False
         self.live: Dict[object, RequestCache] = {}
+        # for tests: set `owners` to a dict and every hand-out of a page is logged there as
+        # (group, page) -> [request ids in the order they held it]
+        self.owners: Dict[tuple, list] | None = None
         keys: Dict[PagedKVNeed, int] = {}
         for i, need in enumerate(needs):
             if need is None:
@@ -151,10 +154,14 @@ class CacheManager:
             if n > g.pool.n_free:
                 raise OutOfPages(f"request {rc.request_id!r} needs {n} more page(s) for {n_new} token(s); "
                                  f"{g.pool.n_free} of {g.pool.n_units} free")
-        for g, n, table in zip(self.groups, need, rc.tables):
+        for gi, (g, n, table) in enumerate(zip(self.groups, need, rc.tables)):
             if n:
-                table.extend(g.pool.take(n))
+                pages = g.pool.take(n)
+                table.extend(pages)
                 rc.stamp += 1
+                if self.owners is not None:
+                    for pg in pages:
+                        self.owners.setdefault((gi, pg), []).append(rc.request_id)
         rc.reserved += n_new
 
     def cancel(self, rc: RequestCache) -> None:

@@ -117,14 +117,14 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, Ou
 extern "C" int tuff_rmsnorm(const void* x, int x_dtype, const float* w, void* out, int out_dtype,
                             const int* row_index, int n_rows, int d, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (x_dtype == TUFF_F32 && n_rows > 16 && d % 4 == 0 && d <= 128 * RMS_VEC && !((uintptr_t)x & 15) &&
+    // The warp-per-row kernel adds a row's squares in another order than the block-per-row kernel.  Which of
+    // the two runs depends on the number of rows, so only the bf16 path may use it: the 32-bit path gives
+    // the same bits for a row whatever else is in the batch.
+    if (x_dtype == TUFF_F32 && out_dtype == TUFF_BF16 && n_rows > 16 && d % 4 == 0 && d <= 128 * RMS_VEC && !((uintptr_t)x & 15) &&
         !((uintptr_t)w & 15) && !((uintptr_t)out & 15)) {
         const int warps = n_rows >= 2048 ? 8 : n_rows >= 512 ? 4 : n_rows >= 128 ? 2 : 1;
         const dim3 grid(ceil_div(n_rows, warps)), block(32 * warps);
-        if (out_dtype == TUFF_BF16)
-            return launch_pdl(rmsnorm_rows_kernel<bf16>, grid, block, 0, stream, (const float*)x, w, (bf16*)out, row_index, n_rows, d, eps);
-        if (out_dtype == TUFF_F32)
-            return launch_pdl(rmsnorm_rows_kernel<float>, grid, block, 0, stream, (const float*)x, w, (float*)out, row_index, n_rows, d, eps);
+        return launch_pdl(rmsnorm_rows_kernel<bf16>, grid, block, 0, stream, (const float*)x, w, (bf16*)out, row_index, n_rows, d, eps);
     }
     const int threads = 256;
     int rc = 0;
