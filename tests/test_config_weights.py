@@ -35,6 +35,13 @@ def test_lfm2_config_fields():
     assert Lfm2Config.from_dict(a.to_dict()) == a and Lfm2Config.from_dict(b.to_dict()) == b
 
 
+def test_both_names_of_the_ffn_width():
+    same = dict(TINY_A, block_ff_dim=TINY_A["intermediate_size"])
+    assert config_from_dict(same)[1].ffn_dim == config_from_dict(TINY_A)[1].ffn_dim
+    only = {k: v for k, v in same.items() if k != "intermediate_size"}
+    assert config_from_dict(only)[1].ffn_dim == config_from_dict(TINY_A)[1].ffn_dim
+
+
 def test_lfm2_1p2b_shape():
     raw = dict(architectures=["Lfm2ForCausalLM"], hidden_size=2048, num_hidden_layers=16, num_attention_heads=32,
                num_key_value_heads=8, intermediate_size=8192, block_auto_adjust_ff_dim=True, block_multiple_of=256,
@@ -60,6 +67,7 @@ def test_lfm2_1p2b_shape():
     (lambda c: c.update(architectures=["NoSuchModel"]), "not registered"),
     (lambda c: (c.pop("layer_types"),), "layer_types"),
     (lambda c: c.update(hidden_size=66), "head_dim"),
+    (lambda c: c.update(block_ff_dim=c["intermediate_size"] + 64), "block_ff_dim"),
 ])
 def test_config_errors(mutate, word):
     c = copy.deepcopy(TINY_A)

@@ -75,35 +75,6 @@ def test_linear(dtype, M, N, K):
     close(logits, ref, "float32", scale=4.0 if dtype == "float32" else 1.0)   # fp32 out even from bf16 operands
 
 
-def test_linear_by_cta_pairs():
-    """The tensor-core product computed by pairs of CTAs (an option, off by default): ragged sizes
-    against fp64, in a process of its own since the switch is read once."""
-    import subprocess, sys, os
-    code = """
-import numpy as np, torch
-from tuff_b200.kernels import ops
-rng = np.random.default_rng(41)
-for M, N, K in ((300, 520, 136), (512, 2048, 192), (257, 129, 72), (1100, 777, 2048)):
-    a = torch.tensor(rng.normal(size=(M, K)), dtype=torch.bfloat16, device='cuda')
-    w = torch.tensor(rng.normal(size=(N, K)) * 0.05, dtype=torch.bfloat16, device='cuda')
-    ref = a.double().cpu().numpy() @ w.double().cpu().numpy().T
-    out = torch.empty(M, N, dtype=torch.bfloat16, device='cuda')
-    ops.gemm_tc(a, w, out)
-    acc = torch.ones(M, N, device='cuda')
-    ops.gemm_tc(a, w, acc, accumulate=True)
-    ops.check_tc_status()
-    tol = 2e-2 * max(1.0, np.abs(ref).max())
-    assert np.abs(out.double().cpu().numpy() - ref).max() <= 2 * tol, (M, N, K)
-    assert np.abs(acc.double().cpu().numpy() - 1 - ref).max() <= 1e-3 * max(1.0, np.abs(ref).max()), (M, N, K)
-print('pairs ok')
-"""
-    env = dict(os.environ, TUFF_GEMM_PAIR="1")
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
-    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
-    assert r.returncode == 0 and "pairs ok" in r.stdout, r.stdout + r.stderr
-
-
 def test_linear_is_batch_invariant():
     """A row's fp32 result does not depend on how many rows run with it."""
     from tuff_b200.kernels import ops
@@ -236,6 +207,13 @@ def test_qk_norm_rope_write_and_attention(dtype, H, G, hd, page, rot, blocked):
             ref[:, h] = (p / p.sum(-1, keepdims=True)) @ v[:, g]
         close(out[o:o + lens[r]], ref[starts[r]:].reshape(lens[r], H * hd), dtype, scale=3.0)
         o += lens[r]
+        # the keys in the pages carry the rotation of their absolute positions (the scores above see only
+        # differences of positions, so they cannot tell), and the values lie where the table says
+        kd, vd = kp.double().cpu().numpy(), vp.double().cpu().numpy()
+        for pos in sorted({0, seqs[r] // 2, seqs[r] - 1}):
+            pg, off = table[r][pos // page], pos % page
+            close(torch.as_tensor(kd[pg, :, off]), k[pos], dtype, scale=2.0)
+            close(torch.as_tensor(vd[pg, :, off]), v[pos], dtype, scale=2.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -109,6 +109,25 @@ def test_preempted_request_recomputes_prompt_plus_outputs():
     assert b.output == [1000 + i for i in range(6)] and a.output == [1000 + i for i in range(6)]
 
 
+def test_preempted_request_returns_to_the_head_of_the_queue():
+    """A request that had to give its pages back is admitted again before requests that came after it."""
+    cm, sch = make(max_tokens=32, page_size=4, budget=64, max_running=2)   # 8 pages, two may run
+    sch.add("a", list(range(14)), SamplingParams(max_new_tokens=8))
+    sch.add("b", list(range(100, 114)), SamplingParams(max_new_tokens=8))
+    sch.add("c", list(range(200, 206)), SamplingParams(max_new_tokens=2))
+    order, hit = [], False
+    steps = 0
+    while sch.has_work():
+        plan, done = run_step(cm, sch)
+        order += [r.request_id for r in plan.admitted]
+        for r in plan.preempted:
+            hit = True
+            assert [w.request_id for w in sch.waiting][:2] == [r.request_id, "c"]
+        steps += 1
+        assert steps < 300
+    assert hit and order.index("c") > max(i for i, rid in enumerate(order) if rid == "b")
+
+
 def test_errors():
     cm, sch = make(max_tokens=16, ctx=32)
     with pytest.raises(SchedulerError):

@@ -103,6 +103,10 @@ class Lfm2Config:
             hd = d // H
         V = r.integer("vocab_size", min_value=1)
         inter = r.integer("intermediate_size", "block_ff_dim", min_value=1)
+        if r.has("intermediate_size") and r.has("block_ff_dim") and r.integer("block_ff_dim") != inter:
+            # two names of one size; which of them would win is not for this reader to guess
+            raise ConfigError(f"{where}: intermediate_size {inter} and block_ff_dim {r.integer('block_ff_dim')} "
+                              f"name the same feed-forward width and disagree; keep one of them")
         auto = r.boolean("block_auto_adjust_ff_dim", default=False)
         mult = r.optional_number("ffn_dim_multiplier", "block_ffn_dim_multiplier")
         mof = r.integer("block_multiple_of", default=256, min_value=1)

@@ -22,6 +22,15 @@ from .runner import ModelRunner
 from .scheduler import Request, Scheduler, StepPlan
 
 
+class _Result:
+    """A step's sampled ids: on the device (the next step may take its input from there), and the pinned
+    host buffer they are being copied to with the event that says the copy is done."""
+    __slots__ = ("ids", "host", "n", "copied")
+
+    def __init__(self, ids, host, n, copied):
+        self.ids, self.host, self.n, self.copied = ids, host, n, copied
+
+
 class Engine:
     def __init__(self, model_dir: str | None, dtype="bfloat16", device="cuda:0", ctx_size: int | None = None,
                  max_tokens: int | None = None, page_size: int = 64, max_batched_tokens: int = 2048,
@@ -42,7 +51,12 @@ class Engine:
         self.sampler = Sampler(self.runner.vocab_size, self.runner.device)
         self.timing: Dict[str, float] = dict(steps=0, step_seconds=0.0)
         self.run_ahead = bool(run_ahead)
-        self._ahead = None            # (plan, sampled ids on the device) of a step launched and not yet read
+        self._ahead = None            # (plan, its `_Result`) of a step launched and not yet read
+        # Sampled ids come back on a stream of their own: the copy of step N waits for step N's sampling
+        # only, so the host reads it while step N+1, already queued on the compute stream, runs.
+        self._copy_stream = torch.cuda.Stream(device=self.runner.device)
+        self._host_ids = [torch.empty(max_running + 1, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._host_next = 0
 
     @property
     def config(self):
@@ -68,28 +82,47 @@ class Engine:
         host to plan, lay out and launch.  The host learns the ids one step late; a request that
         turns out to have met a stop token has run one step too many, whose result is dropped."""
         if self._ahead is not None:
-            plan, sampled_dev = self._ahead
+            plan, result = self._ahead
             self._ahead = None
         else:
             plan = self.scheduler.plan()
             if not plan.entries:
                 return []
-            sampled_dev = self._launch(plan, None)
+            result = self._launch(plan, None)
         nxt = None
-        if self.run_ahead and sampled_dev is not None and self._may_run_ahead(plan):
+        if self.run_ahead and result is not None and self._may_run_ahead(plan):
             nxt_plan = self.scheduler.plan_ahead(plan)
             if nxt_plan is not None:
-                nxt = (nxt_plan, self._launch(nxt_plan, sampled_dev))
-        sampled = self._read_ids(sampled_dev) if sampled_dev is not None else []
+                nxt = (nxt_plan, self._launch(nxt_plan, result.ids))
+        sampled = self._read_ids(result) if result is not None else []
         finished = self.scheduler.update(plan, sampled)
         if nxt is not None and self.scheduler.running:
             self._ahead = nxt
         return finished
 
-    def _read_ids(self, sampled_dev: torch.Tensor) -> List[int]:
-        """The sampled ids on the host, read together with the kernels' status word (one copy, one wait):
-        a kernel whose bounded wait ran out has left a code there, and what the step wrote is invalid."""
-        both = torch.cat([sampled_dev.view(-1), ops.status_word(self.runner.device)]).tolist()
+    def _send_home(self, ids: torch.Tensor) -> "_Result":
+        """Starts the copy of a step's sampled ids, and of the kernels' status word behind them, into pinned
+        host memory on the copy stream, which waits for the sampling only: not for what the compute stream is
+        given afterwards."""
+        n = ids.numel()
+        host = self._host_ids[self._host_next]
+        self._host_next = (self._host_next + 1) % len(self._host_ids)
+        sampled = torch.cuda.Event()
+        sampled.record()
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(sampled)
+            host[:n].copy_(ids.view(-1), non_blocking=True)
+            host[n:n + 1].copy_(ops.status_word(self.runner.device), non_blocking=True)
+            copied = torch.cuda.Event()
+            copied.record()
+        return _Result(ids, host, n, copied)
+
+    def _read_ids(self, result: "_Result") -> List[int]:
+        """The sampled ids on the host, read together with the kernels' status word (one wait, on the copy's
+        own event): a kernel whose bounded wait ran out has left a code there, and what the step wrote is
+        invalid."""
+        result.copied.synchronize()
+        both = result.host[:result.n + 1].tolist()
         if both[-1]:
             self.reset()
             ops.raise_on_status(both[-1])
@@ -108,10 +141,10 @@ class Engine:
         return all(not (e.request.params.repeat_penalty > 1.0 and e.request.params.repeat_last_n
                         and not e.request.params.greedy) for e in plan.entries)
 
-    def _launch(self, plan: StepPlan, token_source) -> torch.Tensor | None:
-        """Runs the plan's step and samples; returns the sampled ids, still on the device (None if
-        no entry samples).  `token_source`: the ids sampled by the step before, for a plan made
-        ahead of them."""
+    def _launch(self, plan: StepPlan, token_source) -> "_Result | None":
+        """Runs the plan's step and samples; returns the sampled ids, on the device and on their way to
+        the host (None if no entry samples).  `token_source`: the ids sampled by the step before, on the
+        device, for a plan made ahead of them."""
         t0 = time.perf_counter()
         ahead = token_source is not None
         entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.samples else [])
@@ -125,7 +158,7 @@ class Engine:
                 n_all = len(r.prompt) + len(r.output)
                 recent = r.token_slice(n_all - p.repeat_last_n) if (p.repeat_penalty > 1.0 and p.repeat_last_n) else ()
                 rows.append(SampleRow(p, r.key, len(r.output) + (1 if ahead else 0), recent))
-        out = self.sampler.sample(logits, rows) if rows else None
+        out = self._send_home(self.sampler.sample(logits, rows)) if rows else None
         self.timing["steps"] += 1
         self.timing["step_seconds"] += time.perf_counter() - t0
         return out
