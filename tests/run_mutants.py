@@ -18,7 +18,7 @@ import sys
 import tempfile
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CPU_TESTS = ("tests/test_scheduler.py", "tests/test_cache_manager.py", "tests/test_config_weights.py", "tests/test_plain.py")
+CPU_TESTS = ("tests/test_scheduler.py", "tests/test_cache_manager.py", "tests/test_config_weights.py", "tests/test_plain.py", "tests/test_index_helpers.py")
 
 
 def read_mutants(path):

@@ -133,3 +133,24 @@ def test_trace_run_program(models, tmp_path, dtype):
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
     compare(str(out), wanted, expect, CONFIGS["tiny_b"][0]["vocab_size"], dtype, "trace_run mixed")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_range_checking_build_finds_nothing_on_a_mixed_trace(models, tmp_path, dtype):
+    """The build whose kernels range-check every table row, page id and state slot they are given
+    (TUFF_DEBUG_BOUNDS=1), as a program over a mixed trace with reused pages: it ends without a code in the
+    status word (trace_run reads it after every step) and writes the very logits of the normal build."""
+    folder, reqs, expect = models["tiny_d"]
+    steps, wanted = traces.mixed(reqs, seed=5)
+    text = "\n".join(json.dumps(s) for s in steps) + "\n"
+    outs = {}
+    for name, env in (("normal", {}), ("checked", {"TUFF_DEBUG_BOUNDS": "1"})):
+        out = tmp_path / name
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                               "--out", str(out), "--max-tokens", str(traces.tokens_needed(steps))],
+                              input=text, text=True, capture_output=True, timeout=1500, env={**os.environ, **env})
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        outs[name] = logits_by_place(str(out), wanted, CONFIGS["tiny_d"][0]["vocab_size"])
+    compare(str(tmp_path / "checked"), wanted, expect, CONFIGS["tiny_d"][0]["vocab_size"], dtype, "checked build")
+    for place, row in outs["normal"].items():
+        assert np.array_equal(row.view(np.uint32), outs["checked"][place].view(np.uint32)), place

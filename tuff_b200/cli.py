@@ -63,6 +63,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--num-pages", type=int, default=None, help="cache pages (default: enough for one full context)")
     ap.add_argument("--max-batched-tokens", type=int, default=2048)
+    ap.add_argument("--max-running", type=int, default=4, help="requests that may be live at once (default: 4)")
     ap.add_argument("--device", default="cuda:0")
     return ap
 
@@ -169,7 +170,7 @@ def run(args, model_dir: str) -> int:
     budget = args.prefill_batch or args.max_batched_tokens
     max_tokens = args.num_pages * args.page_size if args.num_pages else args.ctx
     engine = Engine(model_dir, dtype=args.dtype, device=args.device, ctx_size=args.ctx, max_tokens=max_tokens,
-                    page_size=args.page_size, max_batched_tokens=budget, max_running=4)
+                    page_size=args.page_size, max_batched_tokens=budget, max_running=max(1, args.max_running))
     print(f"[tuff] prompt: {len(prompt)} tokens: {' '.join(map(str, prompt[:32]))}{' ...' if len(prompt) > 32 else ''}",
           file=sys.stderr)
     sp = SamplingParams(temp=args.temp, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,

@@ -206,12 +206,3 @@ class Lfm2Config:
         d["full_attn_idxs"] = list(self.full_attn_idxs)
         d.pop("ignored_keys", None)
         return d
-
-
-# The sizes of LFM2.5-1.2B as a config.json dictionary (no weights): what the benchmark and the
-# kernel probes build their random-weights model from.
-LFM2_1P2B_SHAPE = dict(
-    architectures=["Lfm2ForCausalLM"], hidden_size=2048, num_hidden_layers=16, num_attention_heads=32,
-    num_key_value_heads=8, intermediate_size=8192, block_auto_adjust_ff_dim=True, block_multiple_of=256,
-    vocab_size=65536, rope_theta=1e6, norm_eps=1e-5, conv_L_cache=3, full_attn_idxs=[2, 5, 8, 10, 12, 14],
-    tie_embedding=True, max_position_embeddings=128000)

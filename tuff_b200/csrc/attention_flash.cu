@@ -23,6 +23,7 @@
 // so stale or never-written cache contents (even NaN) are harmless.
 // Every mbarrier wait is bounded; a wait that runs out records a code in *status.
 #include "sm100.cuh"
+#include "index.cuh"
 
 namespace {
 constexpr int TILE = 64;                 // keys per tile
@@ -137,6 +138,7 @@ __device__ __forceinline__ void process_tile(uint32_t sK, uint32_t sV, const uin
 struct AttnParams {
     const bf16* q; long long q_stride;
     const int* block_table; int max_blocks;
+    long long n_pages;            // pages in the pool (read by a checked build only)
     const int* positions; const int* row_of_token; const int* cu_q;
     bf16* out;                       // [T, H*HD]
     float* part_o; float* part_ml;   // decode: [T, H, splits, HD] and [T, H, splits, 2]
@@ -149,12 +151,16 @@ struct AttnParams {
 template <int HD>
 __device__ __forceinline__ void load_tile(const CUtensorMap* mk, const CUtensorMap* mv, uint32_t sK, uint32_t sV,
                                           uint32_t bar, const int* bt, int max_blocks, int tile, int g, int G,
-                                          int page_size) {
+                                          int page_size, long long n_pages, int* status) {
     mbar_expect_tx(bar, 2 * TILE * HD * 2);
     const int pages = TILE / page_size;
     for (int i = 0; i < pages; ++i) {
         const int blk = tile * pages + i;
-        const int page = blk < max_blocks ? ld_act(bt + blk) : -1;    // beyond the row's table: no page
+        int page = blk < max_blocks ? ld_act(bt + blk) : -1;          // beyond the row's table: no page
+        if (TUFF_CHECKED && page != -1 && !page_ok(page, n_pages)) {  // (a load outside the tensor is harmless: it reads zeros)
+            bounds_fault(Bounds{0, n_pages, status}, TUFF_BOUNDS_PAGE);
+            page = -1;
+        }
         const int y = (page * G + g) * page_size;            // a missing page (-1) lies outside the tensor: zero fill
 #pragma unroll
         for (int h = 0; h < HD / 64; ++h) {
@@ -209,7 +215,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
                 const int s = i % DEC_STAGES;
                 if (!mbar_wait(bars + 8 * (DEC_STAGES + s), ((i / DEC_STAGES) & 1) ^ 1, p.status, 11)) { ok = false; break; }
                 load_tile<HD>(&mk, &mv, base + s * STAGE_BYTES, base + s * STAGE_BYTES + TILE * HD * 2, bars + 8 * s, bt,
-                              p.max_blocks, t_begin + i, g, p.G, p.page_size);
+                              p.max_blocks, t_begin + i, g, p.G, p.page_size, p.n_pages, p.status);
             }
         }
     } else {
@@ -340,7 +346,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
                 const int s = i % PRE_STAGES;
                 if (!mbar_wait(bars + 8 * (PRE_STAGES + s), ((i / PRE_STAGES) & 1) ^ 1, p.status, 21)) { ok = false; break; }
                 load_tile<HD>(&mk, &mv, base + s * STAGE_BYTES, base + s * STAGE_BYTES + TILE * HD * 2, bars + 8 * s, bt,
-                              p.max_blocks, tile_lo + i, g, p.G, p.page_size);
+                              p.max_blocks, tile_lo + i, g, p.G, p.page_size, p.n_pages, p.status);
             }
         }
     } else if (warp < n_cons) {
@@ -460,7 +466,7 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
     const long long rows = num_pages * G * page_size;
     if (!pool_map(&mk, k_pages, rows, hd, page_size) || !pool_map(&mv, v_pages, rows, hd, page_size)) return TUFF_E_ALIGN;
     AttnParams p{};
-    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks; p.n_pages = num_pages;
     p.positions = positions; p.row_of_token = row_of_token; p.out = (bf16*)out; p.status = status;
     p.part_o = workspace; p.part_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * hd : nullptr;
     p.n_tokens = n_tokens; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
@@ -498,7 +504,7 @@ extern "C" int tuff_attention_prefill(const void* q, long long q_stride, const v
     const long long rows = num_pages * G * page_size;
     if (!pool_map(&mk, k_pages, rows, hd, page_size) || !pool_map(&mv, v_pages, rows, hd, page_size)) return TUFF_E_ALIGN;
     AttnParams p{};
-    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks; p.n_pages = num_pages;
     p.positions = positions; p.row_of_token = row_of_token; p.cu_q = cu_q; p.out = (bf16*)out; p.status = status;
     p.n_tokens = n_tokens; p.n_rows = n_rows; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.n_splits = 1;
     p.scale_log2 = scale * 1.4426950408889634f;

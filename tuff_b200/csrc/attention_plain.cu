@@ -17,6 +17,7 @@
 // depends on the key's index alone, so a token's result does not depend on how
 // the batch was cut.
 #include "common.cuh"
+#include "index.cuh"
 
 namespace {
 constexpr int MAX_HD = 256;
@@ -34,7 +35,7 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
                           const int* __restrict__ positions, const int* __restrict__ row_of_token,
                           const int* __restrict__ block_table, int max_blocks,
                           T* __restrict__ k_pages, T* __restrict__ v_pages,
-                          int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv) {
+                          int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv, Bounds bounds) {
     constexpr int UNROLL = 4;                        // heads in flight per warp
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,9 +49,17 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
     size_t page_base = 0;
     int in_page = 0;
     if (write_kv) {
-        const int page = ld_act(block_table + (size_t)r * max_blocks + pos / page_size);
-        in_page = pos % page_size;
-        page_base = (size_t)page * G;
+        long long page = -1;
+        if (check_row(bounds, r) && check_entry(bounds, pos, page_size, max_blocks)) {
+            page = ld_act(block_table + (size_t)r * max_blocks + page_entry(pos, page_size));
+            if (!check_page(bounds, page)) page = -1;
+        }
+        if (TUFF_CHECKED && page < 0) {
+            write_kv = 0;                            // a checked build leaves the pages alone and says so
+        } else {
+            in_page = page_offset(pos, page_size);
+            page_base = (size_t)page * G;
+        }
     }
     // this lane's pairs: element indices and rotation
     int e1[PPL], e2[PPL];
@@ -129,7 +138,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
                              const T* __restrict__ v_pages, const int* __restrict__ block_table,
                              int max_blocks, const int* __restrict__ positions,
                              const int* __restrict__ row_of_token, T* __restrict__ out,
-                             int H, int G, int hd, int page_size, float scale, int window) {
+                             int H, int G, int hd, int page_size, float scale, int window, Bounds bounds) {
     __shared__ float sh_acc[ATT_WARPS][MAX_HD];
     __shared__ float sh_m[ATT_WARPS], sh_l[ATT_WARPS];
     const int t = blockIdx.x, h = blockIdx.y;
@@ -137,6 +146,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
     const int g = h / (H / G);
     const int pos = positions[t];
     const int r = row_of_token[t];
+    if (!check_row(bounds, r)) return;               // the same for the whole block
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int* bt = block_table + (size_t)r * max_blocks;
 
@@ -150,8 +160,10 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
     }
     float m = -INFINITY, l = 0.f;
     for (int j = lo + warp; j <= pos; j += ATT_WARPS) {
-        const int page = bt[j / page_size];
-        const size_t off = (((size_t)page * G + g) * page_size + (j % page_size)) * hd;
+        if (!check_entry(bounds, j, page_size, max_blocks)) continue;     // j is the same for the whole warp
+        const int page = bt[page_entry(j, page_size)];
+        if (!check_page(bounds, page)) continue;
+        const size_t off = page_elem(page, g, page_offset(j, page_size), G, page_size, hd);
         const T* kp = k_pages + off;
         const T* vp = v_pages + off;
         float s = 0.f;
@@ -207,7 +219,8 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
                                        const float* inv_freq, const int* positions, const int* row_of_token,
                                        const int* block_table, int max_blocks, void* k_pages, void* v_pages,
                                        int n_tokens, int H, int G, int hd, int rot_dim, int page_size,
-                                       float eps, int write_kv, cudaStream_t stream) {
+                                       float eps, int write_kv, long long table_rows, long long n_pages, int* status,
+                                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd < 2 || hd > MAX_HD || (hd & 1) || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || G < 0 || H < 0) return TUFF_E_SIZE;
     if (write_kv && page_size < 1) return TUFF_E_SIZE;
@@ -218,7 +231,7 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
     dim3 grid(n_tokens, per_token);
 #define QK_GO(T, PPL) return launch_pdl(qk_norm_rope_write_kernel<T, PPL>, grid, dim3(QKV_WARPS * 32), 0, stream, \
         (T*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks, \
-        (T*)k_pages, (T*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv)
+        (T*)k_pages, (T*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv, Bounds{table_rows, n_pages, status})
     if (dtype == TUFF_F32) {
         if (hd <= 64) QK_GO(float, 1); else if (hd <= 128) QK_GO(float, 2); else QK_GO(float, 4);
     } else if (dtype == TUFF_BF16) {
@@ -233,18 +246,19 @@ extern "C" int tuff_paged_attention_plain(const void* q, long long q_stride, con
                                           const void* v_pages, int dtype, const int* block_table, int max_blocks,
                                           const int* positions, const int* row_of_token, void* out,
                                           int n_tokens, int H, int G, int hd, int page_size, float scale,
-                                          int window, cudaStream_t stream) {
+                                          int window, long long table_rows, long long n_pages, int* status,
+                                          cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd < 1 || hd > MAX_HD || G < 1 || H % G != 0 || page_size < 1 || H > 65535) return TUFF_E_SIZE;
     dim3 grid(n_tokens, H);
     if (dtype == TUFF_F32)
         paged_attention_plain_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
             (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_blocks,
-            positions, row_of_token, (float*)out, H, G, hd, page_size, scale, window);
+            positions, row_of_token, (float*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status});
     else if (dtype == TUFF_BF16)
         paged_attention_plain_kernel<bf16><<<grid, ATT_WARPS * 32, 0, stream>>>(
             (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,
-            positions, row_of_token, (bf16*)out, H, G, hd, page_size, scale, window);
+            positions, row_of_token, (bf16*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status});
     else
         return TUFF_E_DTYPE;
     return launch_status();

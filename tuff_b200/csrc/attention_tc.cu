@@ -34,6 +34,7 @@
 // stored.  Every wait is bounded; a wait that runs out records a code in *status, and the CTA
 // still frees its tensor memory.
 #include "sm100.cuh"
+#include "index.cuh"
 
 namespace {
 constexpr int TILE = 64;                 // keys per tile
@@ -44,6 +45,7 @@ constexpr int NUM_THREADS = 192;         // warps 0..3: softmax (TMEM lane quart
 struct TcAttnParams {
     const bf16* q; long long q_stride;
     const int* block_table; int max_blocks;
+    long long n_pages;            // pages in the pool (read by a checked build only)
     const int* positions; const int* cu_q;
     bf16* out;
     int* status;
@@ -166,7 +168,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
                 mbar_expect_tx(kv_full(s), L::STAGE_BYTES);
                 for (int i = 0; i < pages; ++i) {
                     const int bi = (tile_lo + j) * pages + i;
-                    const int page = bi < p.max_blocks ? ld_act(bt + bi) : -1;      // beyond the table: no page
+                    int page = bi < p.max_blocks ? ld_act(bt + bi) : -1;            // beyond the table: no page
+                    if (TUFF_CHECKED && page != -1 && !page_ok(page, p.n_pages)) {  // (a load outside the tensor reads zeros)
+                        bounds_fault(Bounds{0, p.n_pages, p.status}, TUFF_BOUNDS_PAGE);
+                        page = -1;
+                    }
                     const int y = (page * p.G + g) * p.page_size;                   // a missing page lies outside the tensor: zero fill
                     const uint32_t off = (uint32_t)(i * p.page_size) * 128;
                     tma_load_2d(sK + off, &mk, kv_full(s), 0, y);
@@ -372,7 +378,7 @@ extern "C" int tuff_attention_prefill_tc(const void* q, long long q_stride, cons
     const long long rows = num_pages * G * page_size;
     if (!pool_map(&mk, k_pages, rows, hd, page_size) || !pool_map(&mv, v_pages, rows, hd, page_size)) return TUFF_E_ALIGN;
     TcAttnParams p{};
-    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks; p.n_pages = num_pages;
     p.positions = positions; p.cu_q = cu_q; p.out = (bf16*)out; p.status = status;
     p.n_rows = n_rows; p.H = H; p.G = G; p.page_size = page_size; p.window = window;
     p.n_blocks = (n_tokens + QROWS - 1) / QROWS + n_rows;      // an upper bound on the blocks of all requests

@@ -39,6 +39,7 @@
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records a code in *status
 // (61 producer, 63 consumers), stops waiting, and runs to its end.
 #include "sm100.cuh"
+#include "index.cuh"
 #include <algorithm>
 
 namespace {
@@ -67,6 +68,7 @@ struct StreamGemm {
     const float* taps;        // convolution epilogue: [N, L]
     float* state;             // [slots, L-1, N]
     const int* slot_of_row;
+    long long n_slots;        // slots of `state` (read by a checked build only)
     int L;
     // emit (with EPI_ACCUM): the new residual times this norm weight as bf16, and sums of squares per CTA
     const float* emit_w;      // [N] or null
@@ -348,11 +350,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (p.emit_w) pre_emit_w = p.emit_w[col];
             if (p.epi == EPI_CONV && p.L <= MAX_TAPS) {
                 pre_slot = ld_act(p.slot_of_row + tok);
-                const float* stt = p.state + (size_t)pre_slot * (p.L - 1) * p.N;
+                if (check_slot(Bounds{p.M, p.n_slots, p.status}, pre_slot)) {
+                    const float* stt = p.state + slot_elem(pre_slot, (size_t)(p.L - 1) * p.N);
 #pragma unroll
-                for (int j = 0; j < MAX_TAPS; ++j) {
-                    if (j < p.L) pre_taps[j] = p.taps[(size_t)col * p.L + j];
-                    if (j < p.L - 1) pre_state[j] = ld_act(stt + (size_t)j * p.N + col);
+                    for (int j = 0; j < MAX_TAPS; ++j) {
+                        if (j < p.L) pre_taps[j] = p.taps[(size_t)col * p.L + j];
+                        if (j < p.L - 1) pre_state[j] = ld_act(stt + (size_t)j * p.N + col);
+                    }
                 }
             }
         }
@@ -496,7 +500,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const float b = bf16_round(v[0]), cg = bf16_round(v[1]), xg = bf16_round(v[2]);
                 const float u = b * xg;
                 const int L = p.L, d = p.N;
-                float* stt = p.state + (size_t)((fetched && L <= MAX_TAPS) ? pre_slot : ld_act(p.slot_of_row + tok)) * (L - 1) * d;
+                const int slot = (fetched && L <= MAX_TAPS) ? pre_slot : ld_act(p.slot_of_row + tok);
+                if (!check_slot(Bounds{p.M, p.n_slots, p.status}, slot)) continue;      // a checked build leaves this row alone
+                float* stt = p.state + slot_elem(slot, (size_t)(L - 1) * d);
                 float y = 0.f;
                 if (fetched && L <= MAX_TAPS) {
 #pragma unroll
@@ -640,7 +646,7 @@ extern "C" int tuff_gemm_stream_grid(int N) { return N > 0 ? stream_grid(N) : 0;
 // rsqrt(sum over CTAs of scale_part[.][r] / K + scale_eps) before the epilogue.
 extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, const void* W, void* C, int c_dtype,
                                 int M, int N, int K, long long lda, long long ldw, long long ldc, int epilogue,
-                                const float* taps, float* state, const int* slot_of_row, int L, int set_block,
+                                const float* taps, float* state, const int* slot_of_row, long long n_slots, int L, int set_block,
                                 const float* emit_w, void* emit_xw, float* emit_part,
                                 const float* scale_part, int scale_parts, float scale_eps,
                                 int* status, cudaStream_t stream) {
@@ -663,7 +669,7 @@ extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, c
     p.M = M; p.N = N; p.K = K; p.eps = eps; p.epi = epilogue; p.out_dtype = c_dtype;
     p.sets = epilogue == EPI_SWIGLU ? 2 : epilogue == EPI_CONV ? 3 : 1;
     p.set_block = (set_block && p.sets > 1) ? set_block : N;
-    p.taps = taps; p.state = state; p.slot_of_row = slot_of_row; p.L = L;
+    p.taps = taps; p.state = state; p.slot_of_row = slot_of_row; p.n_slots = n_slots; p.L = L;
     p.emit_w = emit_w; p.emit_xw = (bf16*)emit_xw; p.emit_part = emit_part;
     p.scale_part = scale_part; p.scale_parts = scale_parts; p.scale_eps = scale_eps;
     // every SM an equal share of the columns, in passes of at most MAX_ROWS weight rows

@@ -17,6 +17,7 @@
 // taps in ascending order whatever the portion's length, so cutting a prompt
 // differently changes nothing.
 #include "common.cuh"
+#include "index.cuh"
 
 namespace {
 
@@ -24,14 +25,15 @@ template <typename T>
 __global__ void shortconv_fwd_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
                                      const float* __restrict__ state, const int* __restrict__ slot_of_row,
                                      const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
-                                     T* __restrict__ out, int n_tokens, int d, int K) {
+                                     T* __restrict__ out, int n_tokens, int d, int K, Bounds bounds) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int t = blockIdx.x;
     if (c >= d) return;
     const int r = row_of_token[t];
+    if (!check_row(bounds, r) || !check_slot(bounds, slot_of_row[r])) return;
     const int i = t - cu_q[r];                 // index inside this portion
     const size_t ld = (size_t)3 * d;
-    const float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+    const float* st = state + slot_elem(slot_of_row[r], (size_t)(K - 1) * d);
     float y = 0.f;
     for (int j = 0; j < K; ++j) {
         const int back = (K - 1) - j;          // how many tokens before t
@@ -56,14 +58,15 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 __global__ void shortconv_fwd_vec_kernel(const bf16* __restrict__ bcx, const float* __restrict__ taps,
                                          const float* __restrict__ state, const int* __restrict__ slot_of_row,
                                          const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
-                                         bf16* __restrict__ out, int n_tokens, int d, int K) {
+                                         bf16* __restrict__ out, int n_tokens, int d, int K, Bounds bounds) {
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     const int t = blockIdx.x;
     if (c >= d) return;
     const int r = row_of_token[t];
+    if (!check_row(bounds, r) || !check_slot(bounds, slot_of_row[r])) return;
     const int i = t - cu_q[r];
     const size_t ld = (size_t)3 * d;
-    const float* st = state + (size_t)slot_of_row[r] * (K - 1) * d;
+    const float* st = state + slot_elem(slot_of_row[r], (size_t)(K - 1) * d);
     float y[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = 0.f;
@@ -106,7 +109,7 @@ __global__ void __launch_bounds__(128)
 shortconv_fwd_run_kernel(const bf16* __restrict__ bcx, const float* __restrict__ taps,
                          const float* __restrict__ state, const int* __restrict__ slot_of_row,
                          const int* __restrict__ row_of_token, const int* __restrict__ cu_q,
-                         bf16* __restrict__ out, int n_tokens, int d) {
+                         bf16* __restrict__ out, int n_tokens, int d, Bounds bounds) {
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     const int t0 = blockIdx.x * RUN;
     pdl_wait();
@@ -137,9 +140,10 @@ shortconv_fwd_run_kernel(const bf16* __restrict__ bcx, const float* __restrict__
             const int t = tb + q;
             if (t >= t1) break;
             const int r = ld_act(row_of_token + t);
+            if (!check_row(bounds, r) || !check_slot(bounds, ld_act(slot_of_row + r))) return;
             const int i = t - ld_act(cu_q + r);
             if (t == t0 || i == 0) {
-                const float* st = state + (size_t)ld_act(slot_of_row + r) * (K - 1) * d;
+                const float* st = state + slot_elem(ld_act(slot_of_row + r), (size_t)(K - 1) * d);
 #pragma unroll
                 for (int j = 0; j < K - 1; ++j) {
                     const int back = (K - 1) - j;
@@ -188,7 +192,7 @@ shortconv_fwd_run_kernel(const bf16* __restrict__ bcx, const float* __restrict__
 template <typename T>
 __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                        const int* __restrict__ slot_of_row, const int* __restrict__ cu_q,
-                                       int d, int K) {
+                                       int d, int K, Bounds bounds) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int r = blockIdx.x;
     pdl_wait();
@@ -197,7 +201,8 @@ __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restr
     const int q0 = ld_act(cu_q + r), n = ld_act(cu_q + r + 1) - q0;
     if (n <= 0) return;
     const size_t ld = (size_t)3 * d;
-    float* st = state + (size_t)ld_act(slot_of_row + r) * (K - 1) * d;
+    if (!check_slot(bounds, ld_act(slot_of_row + r))) return;
+    float* st = state + slot_elem(ld_act(slot_of_row + r), (size_t)(K - 1) * d);
     for (int s = 0; s < K - 1; ++s) {
         const int i = n - (K - 1) + s;
         float u;
@@ -216,7 +221,7 @@ __global__ void shortconv_state_kernel(const T* __restrict__ bcx, float* __restr
 template <typename T>
 __global__ void shortconv_single_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
                                         float* __restrict__ state, const int* __restrict__ slot_of_row,
-                                        T* __restrict__ out, int d, int K) {
+                                        T* __restrict__ out, int d, int K, Bounds bounds) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int r = blockIdx.x;                       // row r's token is token r
     pdl_wait();
@@ -224,7 +229,8 @@ __global__ void shortconv_single_kernel(const T* __restrict__ bcx, const float* 
     if (c >= d) return;
     const T* p = bcx + (size_t)r * 3 * d;
     const float u = ld_act(p + c) * ld_act(p + 2 * d + c);
-    float* st = state + (size_t)ld_act(slot_of_row + r) * (K - 1) * d;
+    if (!check_slot(bounds, ld_act(slot_of_row + r))) return;
+    float* st = state + slot_elem(ld_act(slot_of_row + r), (size_t)(K - 1) * d);
     float y = 0.f;
     for (int j = 0; j < K - 1; ++j) {
         const float s = ld_act(st + (size_t)j * d + c);
@@ -240,43 +246,45 @@ __global__ void shortconv_single_kernel(const T* __restrict__ bcx, const float* 
 // bcx [n_tokens, 3d], taps [d, K] fp32, state [n_slots, K-1, d] fp32, out [n_tokens, d].
 extern "C" int tuff_shortconv(const void* bcx, void* out, int dtype, const float* taps, float* state,
                               const int* slot_of_row, const int* row_of_token, const int* cu_q,
-                              int n_tokens, int n_rows, int d, int K, int all_single, cudaStream_t stream) {
+                              int n_tokens, int n_rows, int d, int K, int all_single, long long n_slots, int* status,
+                              cudaStream_t stream) {
     if (n_tokens <= 0 || n_rows <= 0) return 0;
     if (K < 2) return TUFF_E_SIZE;
+    const Bounds bounds{n_rows, n_slots, status};        // read by a checked build only
     const int threads = 128;
     if (all_single && n_tokens == n_rows) {
         dim3 g(n_rows, ceil_div(d, threads));
         if (dtype == TUFF_F32)
-            return launch_pdl(shortconv_single_kernel<float>, g, dim3(threads), 0, stream, (const float*)bcx, taps, state, slot_of_row, (float*)out, d, K);
+            return launch_pdl(shortconv_single_kernel<float>, g, dim3(threads), 0, stream, (const float*)bcx, taps, state, slot_of_row, (float*)out, d, K, bounds);
         else if (dtype == TUFF_BF16)
-            return launch_pdl(shortconv_single_kernel<bf16>, g, dim3(threads), 0, stream, (const bf16*)bcx, taps, state, slot_of_row, (bf16*)out, d, K);
+            return launch_pdl(shortconv_single_kernel<bf16>, g, dim3(threads), 0, stream, (const bf16*)bcx, taps, state, slot_of_row, (bf16*)out, d, K, bounds);
         return TUFF_E_DTYPE;
     }
     dim3 g1(n_tokens, ceil_div(d, threads)), g2(n_rows, ceil_div(d, threads));
     if (dtype == TUFF_F32) {
         shortconv_fwd_kernel<float><<<g1, threads, 0, stream>>>((const float*)bcx, taps, state, slot_of_row,
-                                                                 row_of_token, cu_q, (float*)out, n_tokens, d, K);
-        shortconv_state_kernel<float><<<g2, threads, 0, stream>>>((const float*)bcx, state, slot_of_row, cu_q, d, K);
+                                                                 row_of_token, cu_q, (float*)out, n_tokens, d, K, bounds);
+        shortconv_state_kernel<float><<<g2, threads, 0, stream>>>((const float*)bcx, state, slot_of_row, cu_q, d, K, bounds);
     } else if (dtype == TUFF_BF16) {
         const bool vec = d % 8 == 0 && !((uintptr_t)bcx & 15) && !((uintptr_t)out & 15) && !((uintptr_t)state & 15);
         constexpr int RUN = 8;
         const dim3 gr(ceil_div(n_tokens, RUN), ceil_div(d / 8, threads));
         if (vec && n_tokens >= 4 * RUN && K == 3)
             launch_pdl(shortconv_fwd_run_kernel<3, RUN>, gr, dim3(threads), 0, stream, (const bf16*)bcx, taps, (const float*)state, slot_of_row,
-                       row_of_token, cu_q, (bf16*)out, n_tokens, d);
+                       row_of_token, cu_q, (bf16*)out, n_tokens, d, bounds);
         else if (vec && n_tokens >= 4 * RUN && K == 2)
             launch_pdl(shortconv_fwd_run_kernel<2, RUN>, gr, dim3(threads), 0, stream, (const bf16*)bcx, taps, (const float*)state, slot_of_row,
-                       row_of_token, cu_q, (bf16*)out, n_tokens, d);
+                       row_of_token, cu_q, (bf16*)out, n_tokens, d, bounds);
         else if (vec && n_tokens >= 4 * RUN && K == 4)
             launch_pdl(shortconv_fwd_run_kernel<4, RUN>, gr, dim3(threads), 0, stream, (const bf16*)bcx, taps, (const float*)state, slot_of_row,
-                       row_of_token, cu_q, (bf16*)out, n_tokens, d);
+                       row_of_token, cu_q, (bf16*)out, n_tokens, d, bounds);
         else if (vec)
             shortconv_fwd_vec_kernel<<<dim3(n_tokens, ceil_div(d / 8, threads)), threads, 0, stream>>>(
-                (const bf16*)bcx, taps, state, slot_of_row, row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
+                (const bf16*)bcx, taps, state, slot_of_row, row_of_token, cu_q, (bf16*)out, n_tokens, d, K, bounds);
         else
             shortconv_fwd_kernel<bf16><<<g1, threads, 0, stream>>>((const bf16*)bcx, taps, state, slot_of_row,
-                                                                    row_of_token, cu_q, (bf16*)out, n_tokens, d, K);
-        launch_pdl(shortconv_state_kernel<bf16>, g2, dim3(threads), 0, stream, (const bf16*)bcx, state, slot_of_row, cu_q, d, K);
+                                                                    row_of_token, cu_q, (bf16*)out, n_tokens, d, K, bounds);
+        launch_pdl(shortconv_state_kernel<bf16>, g2, dim3(threads), 0, stream, (const bf16*)bcx, state, slot_of_row, cu_q, d, K, bounds);
     } else {
         return TUFF_E_DTYPE;
     }

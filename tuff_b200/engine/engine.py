@@ -52,6 +52,9 @@ class Engine:
         self.timing: Dict[str, float] = dict(steps=0, step_seconds=0.0)
         self.run_ahead = bool(run_ahead)
         self._ahead = None            # (plan, its `_Result`) of a step launched and not yet read
+        # Set to a list to have every step bracketed by CUDA events: (start, end, tokens of the step) is
+        # appended per step; after a synchronize, start.elapsed_time(end) is the step's time on the device.
+        self.step_events: list | None = None
         # Sampled ids come back on a stream of their own: the copy of step N waits for step N's sampling
         # only, so the host reads it while step N+1, already queued on the compute stream, runs.
         self._copy_stream = torch.cuda.Stream(device=self.runner.device)
@@ -149,6 +152,9 @@ class Engine:
         ahead = token_source is not None
         entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                    for e in plan.entries]
+        if self.step_events is not None:
+            ev0 = torch.cuda.Event(enable_timing=True)
+            ev0.record()
         logits = self.runner.step(entries, token_source)
         rows = []
         for e in plan.entries:
@@ -159,6 +165,10 @@ class Engine:
                 recent = r.token_slice(n_all - p.repeat_last_n) if (p.repeat_penalty > 1.0 and p.repeat_last_n) else ()
                 rows.append(SampleRow(p, r.key, len(r.output) + (1 if ahead else 0), recent))
         out = self._send_home(self.sampler.sample(logits, rows)) if rows else None
+        if self.step_events is not None:
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev1.record()
+            self.step_events.append((ev0, ev1, sum(len(e.tokens) for e in plan.entries)))
         self.timing["steps"] += 1
         self.timing["step_seconds"] += time.perf_counter() - t0
         return out

@@ -127,7 +127,7 @@ class ModelRunner:
             self.cache.commit(e.cache, len(e.tokens))
         return logits
 
-    MAX_GRAPHS = 24
+    MAX_GRAPHS = 128
 
     def _run(self, entries: Sequence[StepEntry], token_source: torch.Tensor | None = None) -> torch.Tensor:
         R = len(entries)

@@ -26,6 +26,15 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr"]
 LINK_LIBS: dict[str, list[str]] = {}
+# TUFF_DEBUG_BOUNDS=1 in the environment builds (under names of their own) and loads the variants of these
+# libraries whose kernels range-check every table row, page id and state slot they are given and leave a
+# code in the status word instead of making the access (csrc/index.cuh).
+CHECKED_LIBS = ("attention_plain", "attention_flash", "attention_tc", "shortconv", "gemm_stream")
+
+
+def _flags(name: str) -> list[str]:
+    extra = ["-DTUFF_DEBUG_BOUNDS"] if name in CHECKED_LIBS and os.environ.get("TUFF_DEBUG_BOUNDS", "0") not in ("", "0") else []
+    return NVCC_FLAGS + extra
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -59,7 +68,7 @@ def _digest(name: str) -> str:
             with open(os.path.join(CSRC, f), "rb") as fh:
                 h.update(f.encode())
                 h.update(fh.read())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + LINK_LIBS.get(name, [])).encode())
+    h.update(" ".join(ARCH_FLAGS + _flags(name) + LINK_LIBS.get(name, [])).encode())
     return h.hexdigest()[:16]
 
 
@@ -105,7 +114,7 @@ def compile_library(name: str, verbose: bool = True) -> str:
         return found
     out = library_path(name)
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
-    cmd = [_nvcc()] + ARCH_FLAGS + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src] + LINK_LIBS.get(name, [])
+    cmd = [_nvcc()] + ARCH_FLAGS + _flags(name) + ["-I", CSRC, "-o", tmp, src] + LINK_LIBS.get(name, [])
     t0 = time.time()
     if verbose:
         print(f"[tuff_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
@@ -148,9 +157,24 @@ def load_library(name: str) -> ctypes.CDLL:
         return lib
 
 
-def build_all(verbose: bool = True, jobs: int | None = None) -> list[str]:
-    """Compiles every source (in parallel); used by the build check."""
+def build_all(verbose: bool = True, jobs: int | None = None, checked: bool = False) -> list[str]:
+    """Compiles every source (in parallel); used by the build check.  `checked`: the range-checking
+    variants of `CHECKED_LIBS` instead (what TUFF_DEBUG_BOUNDS=1 loads)."""
     names = sources()
+    if checked:
+        before = os.environ.get("TUFF_DEBUG_BOUNDS")
+        os.environ["TUFF_DEBUG_BOUNDS"] = "1"
+        try:
+            return _build(list(CHECKED_LIBS), verbose, jobs)
+        finally:
+            if before is None:
+                del os.environ["TUFF_DEBUG_BOUNDS"]
+            else:
+                os.environ["TUFF_DEBUG_BOUNDS"] = before
+    return _build(names, verbose, jobs)
+
+
+def _build(names: list[str], verbose: bool, jobs: int | None) -> list[str]:
     jobs = jobs or min(len(names), max(1, (os.cpu_count() or 2)))
     out: dict[str, str] = {}
     errs: list[BaseException] = []

@@ -182,7 +182,9 @@ def tc_status(device=None) -> int:
     in the decode product 61 producer, 63 consumers; in attention 11/12 decode producer/consumer, 21/22 prompt
     portions on mma.sync producer/consumer; in the tcgen05 attention 31 producer, 32-36 MMA issuer
     (query, keys, score buffer, P, -), 37-41 softmax warps (scores, last tile's values, O before a
-    rescale, P buffer, final O)."""
+    rescale, P buffer, final O).  A build with TUFF_DEBUG_BOUNDS=1 also leaves 71 (a position beyond a
+    block table's width), 72 (a page id outside the pool), 73 (a state slot outside the slots) or 74 (a batch
+    row outside the table) where a kernel was given such an index, and skips the access."""
     out = 0
     for dev, st in _tc_state.items():
         if device is None or torch.device(device) == dev:
@@ -196,8 +198,8 @@ def check_tc_status() -> None:
 
 def raise_on_status(code: int) -> None:
     if code:
-        raise KernelError(f"a kernel gave up waiting on a barrier (code {code}, see ops.tc_status); "
-                          "the results of the step are invalid")
+        what = "was given an index outside its range" if 71 <= code <= 74 else "gave up waiting on a barrier"
+        raise KernelError(f"a kernel {what} (code {code}, see ops.tc_status); the results of the step are invalid")
 
 
 def status_word(device) -> torch.Tensor:
@@ -344,7 +346,7 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
                                 c_float(norm.eps if norm is not None else 0.0), _ptr(w), _ptr(out), dtype_code(out),
                                 c_int(M), c_int(N), c_int(K), c_longlong(src.stride(0)), c_longlong(w.stride(0)),
                                 c_longlong(out.stride(0)), c_int(epilogue), _ptr(taps), _ptr(state), _ptr(slots),
-                                c_int(L), c_int(set_block), _ptr(emit_w), _ptr(emit_xw), _ptr(emit_part),
+                                c_longlong(state.shape[0] if state is not None else 0), c_int(L), c_int(set_block), _ptr(emit_w), _ptr(emit_xw), _ptr(emit_part),
                                 _ptr(pre["part"] if pre is not None else None),
                                 c_int(pre["part"].shape[0] if pre is not None else 0),
                                 c_float(pre["eps"] if pre is not None else 0.0),
@@ -434,7 +436,8 @@ def shortconv(bcx: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, slot_o
     lib = load_library("shortconv")
     _check(lib.tuff_shortconv(_ptr(bcx), _ptr(out), dtype_code(out), _ptr(taps), _ptr(state), _ptr(slot_of_row),
                               _ptr(row_of_token), _ptr(cu_q), c_int(n), c_int(n_rows), c_int(d), c_int(K),
-                              c_int(1 if all_single else 0), _stream()), "shortconv", kernels=1 if all_single else 2)
+                              c_int(1 if all_single else 0), c_longlong(state.shape[0]), _ptr(status_word(out.device)),
+                              _stream()), "shortconv", kernels=1 if all_single else 2)
 
 
 # ------------------------------------------------------------------- attention
@@ -467,6 +470,8 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
                                        _ptr(positions), _ptr(row_of_token), _ptr(block_table), c_int(max_blocks),
                                        _ptr(k_pages), _ptr(v_pages), c_int(n), c_int(H), c_int(G), c_int(hd),
                                        c_int(rot_dim), c_int(page_size), c_float(eps), c_int(1 if write_kv else 0),
+                                       c_longlong(block_table.shape[0] if write_kv else 0),
+                                       c_longlong(k_pages.shape[0] if write_kv else 0), _ptr(status_word(qkv.device)),
                                        _stream()), "qk_norm_rope_write")
 
 
@@ -486,7 +491,8 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
                                           dtype_code(q), _ptr(block_table), c_int(block_table.shape[1]),
                                           _ptr(positions), _ptr(row_of_token), _ptr(out), c_int(n), c_int(H),
                                           c_int(G), c_int(hd), c_int(k_pages.shape[2]), c_float(scale),
-                                          c_int(window), _stream()), "paged_attention_plain")
+                                          c_int(window), c_longlong(block_table.shape[0]), c_longlong(k_pages.shape[0]),
+                                          _ptr(status_word(q.device)), _stream()), "paged_attention_plain")
 
 
 _attn_state: dict = {}

@@ -1,5 +1,5 @@
-"""Runs one kernel alone on synthetic data and times it: the command that the summaries under
-`profiles/` were made with, and a quick check of a kernel's bandwidth or throughput.
+"""Runs one kernel alone on synthetic data and times it: a quick check of a kernel's bandwidth or
+throughput, and a small program to put under a profiler.
 
     python -m tuff_b200.kernels.probe gemm_tc --m 2048 --n 11264 --k 2048
     python -m tuff_b200.kernels.probe gemm_decode --m 8 --n 5632 --k 2048 --epilogue swiglu --norm
@@ -7,15 +7,15 @@
     python -m tuff_b200.kernels.probe attention_decode --batch 8 --context 8192
     python -m tuff_b200.kernels.probe attention_prefill --tokens 2048
 
-    python -m tuff_b200.kernels.probe decode_step --batch 8 --context 8192 --steps 6 --no-graphs
-    python -m tuff_b200.kernels.probe prefill_step --tokens 2048 --steps 3
-    python -m tuff_b200.kernels.probe mixed_step --batch 32 --context 4096 --tokens 512 --steps 5
+    python -m tuff_b200.kernels.probe decode_step --config C.json --batch 8 --context 8192 --steps 6 --no-graphs
+    python -m tuff_b200.kernels.probe prefill_step --config C.json --tokens 2048 --steps 3
+    python -m tuff_b200.kernels.probe mixed_step --config C.json --batch 32 --context 4096 --tokens 512 --steps 5
 
 Timing: CUDA events around each launch, after warm-up, with a buffer larger than L2 written
 between launches.  Prints the median time and the achieved rate against the bytes or flops the
 kernel has to move or do.  The `*_step` forms run whole steps of the engine on a random-weights
-model of the LFM2.5-1.2B sizes (contexts filled without computing them) and print the wall time a
-step; under a profiler they give the list of a step's launches.
+model of the sizes in the given config.json (contexts filled without computing them) and print the
+wall time a step; under a profiler they give the list of a step's launches.
 """
 from __future__ import annotations
 
@@ -46,22 +46,27 @@ def timed(fn, reps: int, warmup: int = 3):
 
 
 def run_steps(a) -> int:
-    """Whole steps of the engine on the LFM2.5-1.2B sizes with random weights."""
+    """Whole steps of the engine on a random-weights model of the sizes in `--config`."""
+    import json
     import time
 
     import numpy as np
 
-    from ..config.lfm2 import LFM2_1P2B_SHAPE
+    if not a.config:
+        print("the *_step forms need --config CONFIG.json: the sizes of the model to build", file=sys.stderr)
+        return 2
+    with open(a.config) as f:
+        shape = json.load(f)
     from ..engine import ModelRunner, StepEntry
     from ..engine.engine import Engine
     from ..engine.scheduler import RequestStatus
     from ..sampling import SamplingParams
     rng = np.random.default_rng(0)
-    vocab = LFM2_1P2B_SHAPE["vocab_size"]
+    vocab = shape["vocab_size"]
     if a.kernel == "decode_step":
         n_new = a.steps + 8
         eng = Engine(None, dtype="bfloat16", ctx_size=a.context, max_tokens=a.batch * a.context + 4096, page_size=a.page_size,
-                     max_running=a.batch, config=dict(LFM2_1P2B_SHAPE), cuda_graphs=not a.no_graphs)
+                     max_running=a.batch, config=dict(shape), cuda_graphs=not a.no_graphs)
         for i in range(a.batch):
             r = eng.scheduler.add(i, rng.integers(0, vocab, a.context - n_new).tolist(), SamplingParams(max_new_tokens=n_new))
             eng.scheduler.waiting.remove(r)
@@ -82,7 +87,7 @@ def run_steps(a) -> int:
         return 0
     if a.kernel == "prefill_step":
         runner = ModelRunner(None, dtype="bfloat16", max_tokens=a.tokens + 4096, page_size=a.page_size, max_requests=4,
-                             max_context=a.tokens + 64, config=dict(LFM2_1P2B_SHAPE))
+                             max_context=a.tokens + 64, config=dict(shape))
         for i in range(a.steps):
             rc = runner.open(i)
             toks = rng.integers(0, vocab, a.tokens).tolist()
@@ -97,7 +102,7 @@ def run_steps(a) -> int:
     # mixed_step: decoding rows first, one portion of a prompt after them, as the scheduler lays a step out
     ctx_max = a.context + a.tokens * (a.steps + 4) + 64
     runner = ModelRunner(None, dtype="bfloat16", max_tokens=a.batch * (a.context + 256) + ctx_max, page_size=a.page_size,
-                         max_requests=a.batch + 1, max_context=ctx_max, config=dict(LFM2_1P2B_SHAPE))
+                         max_requests=a.batch + 1, max_context=ctx_max, config=dict(shape))
     rows = [runner.open(i) for i in range(a.batch)]
     for rc in rows:
         runner.synthetic_fill(rc, a.context)
@@ -123,6 +128,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["gemm_tc", "gemm_decode", "decode_chain", "attention_decode", "attention_prefill",
                                        "decode_step", "prefill_step", "mixed_step"])
+    ap.add_argument("--config", help="*_step: a config.json with the sizes of the model")
     ap.add_argument("--layers", type=int, default=16, help="decode_chain: layers of four products each")
     ap.add_argument("--ffn", type=int, default=5632, help="decode_chain: width of the feed-forward")
     ap.add_argument("--steps", type=int, default=8)
