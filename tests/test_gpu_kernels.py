@@ -528,3 +528,86 @@ def test_linear_swiglu_blocked_layout(dtype, M, F, K):
     ops.linear_swiglu(a, w13, out, block)
     close(out, ref, dtype, scale=2.0)
     ops.check_tc_status()
+
+
+# ---- the product of 17 to 128 tokens: K split over a thread-block cluster, sums met in distributed shared memory
+@pytest.mark.parametrize("M,N,K", [(17, 2048, 2048), (64, 2048, 5632), (33, 384, 200), (128, 6144, 2048), (100, 520, 1000),
+                                   (40, 130, 264), (64, 2048, 8192), (96, 3072, 2048), (20, 128, 64)])
+def test_gemm_cluster_store_and_accumulate(M, N, K):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(31)
+    a = dev(rng.normal(size=(M, K)), torch.bfloat16)
+    w = dev(rng.normal(size=(N, K)) * 0.05, torch.bfloat16)
+    assert ops._cluster_eligible(a, w, torch.empty(M, N, dtype=torch.bfloat16, device="cuda"), ops.EPI_STORE)
+    ref = a.double().cpu().numpy() @ w.double().cpu().numpy().T
+    for dt in ("bfloat16", "float32"):
+        out = torch.full((M, N), float("nan"), dtype=DT[dt], device="cuda")
+        ops.gemm_cluster(a, w, out, ops.EPI_STORE)
+        close(out, ref, "bfloat16" if dt == "bfloat16" else "float32", scale=8.0 if dt == "float32" else 1.0)
+    x0 = dev(rng.normal(size=(M, N)) * 2)
+    x = x0.clone()
+    ops.gemm_cluster(a, w, x, ops.EPI_ACCUM)
+    close(x, x0.double().cpu().numpy() + ref, "float32", scale=8.0)
+    # the sums are added in a fixed order: the same bits every time
+    y = x0.clone()
+    ops.gemm_cluster(a, w, y, ops.EPI_ACCUM)
+    assert torch.equal(x, y)
+    # a view with a row stride of its own
+    wide = torch.full((M, N + 24), float("nan"), dtype=torch.float32, device="cuda")
+    ops.linear(a, w, wide[:, 8:8 + N])
+    close(wide[:, 8:8 + N], ref, "float32", scale=8.0)
+    assert torch.isnan(wide[:, :8]).all() and torch.isnan(wide[:, 8 + N:]).all()
+    ops.check_tc_status()
+
+
+@pytest.mark.parametrize("M,F,K", [(17, 256, 96), (64, 5632, 2048), (128, 8192, 2048), (50, 1280, 264)])
+def test_gemm_cluster_swiglu(M, F, K):
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(32)
+    w1 = dev(rng.normal(size=(F, K)) * 0.05, torch.bfloat16)
+    w3 = dev(rng.normal(size=(F, K)) * 0.05, torch.bfloat16)
+    a = dev(rng.normal(size=(M, K)), torch.bfloat16)
+    w13, block = ops.stack_gate_up(w1, w3)
+    assert block == 128
+    g = (a.double() @ w1.double().T).to(torch.bfloat16).double().cpu().numpy()
+    u = (a.double() @ w3.double().T).to(torch.bfloat16).double().cpu().numpy()
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops._cluster_eligible(a, w13, out, ops.EPI_SWIGLU)
+    ops.linear_swiglu(a, w13, out, block)
+    close(out, g / (1 + np.exp(-g)) * u, "bfloat16")
+    ops.check_tc_status()
+
+
+@pytest.mark.parametrize("M,d,K,F", [(64, 2048, 2048, 5632), (17, 264, 96, 256), (128, 2048, 5632, 1024), (37, 1000, 80, 384)])
+def test_gemm_cluster_norm_split_over_two_products(M, d, K, F):
+    """The product that adds into the residual prepares the RMSNorm that follows (bf16(x * w), sums of squares per
+    CTA and token); the products that consume the norm scale their tokens' results: against fp64."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(33)
+    a = dev(rng.normal(size=(M, K)), torch.bfloat16)
+    w1 = dev(rng.normal(size=(d, K)) * 0.05, torch.bfloat16)
+    x0 = dev(rng.normal(size=(M, d)) * 2)
+    nw = dev(1 + 0.1 * rng.normal(size=d))
+    wg, wu = dev(rng.normal(size=(F, d)) * 0.05, torch.bfloat16), dev(rng.normal(size=(F, d)) * 0.05, torch.bfloat16)
+    eps = 1e-5
+    x = x0.clone()
+    ops.announce_norm(x, nw, eps)
+    ops.linear(a, w1, x, accumulate=True)
+    x_ref = x0.double().cpu().numpy() + a.double().cpu().numpy() @ w1.double().cpu().numpy().T
+    close(x, x_ref, "float32", scale=8.0)
+    lazy = ops.NormedRows(x, nw, eps, torch.bfloat16)
+    assert lazy.pre is not None and lazy.pre["part"].shape[1] == M
+    x64 = x.double().cpu().numpy()
+    h = x64 / np.sqrt((x64 ** 2).mean(-1, keepdims=True) + eps) * nw.double().cpu().numpy()
+    out = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear(lazy, wg, out)
+    close(out, h @ wg.double().cpu().numpy().T, "bfloat16", scale=1.5)
+    w13, block = ops.stack_gate_up(wg, wu)
+    act = torch.full((M, F), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear_swiglu(lazy, w13, act, block)
+    g = torch.as_tensor(h @ wg.double().cpu().numpy().T).to(torch.bfloat16).double().numpy()
+    u = torch.as_tensor(h @ wu.double().cpu().numpy().T).to(torch.bfloat16).double().numpy()
+    close(act, g / (1 + np.exp(-g)) * u, "bfloat16", scale=2.0)
+    x.add_(1.0)
+    assert ops.NormedRows(x, nw, eps, torch.bfloat16).pre is None
+    ops.check_tc_status()

@@ -179,7 +179,7 @@ def _tc_buffers(device: torch.device, need_bytes: int):
 def tc_status(device=None) -> int:
     """The status word of the tensor-core kernels (synchronises); non-zero means a bounded wait
     ran out: in the tensor-core product 1 producer, 2 MMA issuer, 3 epilogue, 4 accumulator hand-back;
-    in the decode product 61 producer, 63 consumers; in attention 11/12 decode producer/consumer, 21/22 prompt
+    in the decode product 61 producer, 63 consumers; in the cluster product 51 producer, 52 MMA issuer, 53 epilogue; in attention 11/12 decode producer/consumer, 21/22 prompt
     portions on mma.sync producer/consumer; in the tcgen05 attention 31 producer, 32-36 MMA issuer
     (query, keys, score buffer, P, -), 37-41 softmax warps (scores, last tile's values, O before a
     rescale, P buffer, final O).  A build with TUFF_DEBUG_BOUNDS=1 also leaves 71 (a position beyond a
@@ -237,7 +237,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
                             _ptr(st["status"]), _stream()), "gemm_tc")
 
 
-SKINNY_MAX_TOKENS = 16
+SKINNY_MAX_TOKENS = 16           # the decode product on mma.sync (csrc/gemm_stream.cu)
+CLUSTER_MAX_TOKENS = 128         # the product that splits K over a cluster (csrc/gemm_skinny.cu)
 FUSED_NORM_MAX_K = 2048          # the widest row the fused RMSNorm of a decode product holds in registers
 
 
@@ -254,8 +255,8 @@ _norm_ready: dict = {}
 
 
 def announce_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
-    """The next decode product that adds into `x` (fp32 [M, d], M <= 16) may prepare RMSNorm(x; weight, eps)."""
-    if (x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= SKINNY_MAX_TOKENS
+    """The next product of few tokens that adds into `x` (fp32 [M, d], M <= 128) may prepare RMSNorm(x; weight, eps)."""
+    if (x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= CLUSTER_MAX_TOKENS
             and x.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == x.shape[1]):
         _norm_announced[x.data_ptr()] = (weight, float(eps))
 
@@ -303,7 +304,7 @@ class NormedRows:
         M, K = self.x.shape
         if self.pre is not None:
             return (w.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS and K % 8 == 0 and w.stride(0) % 8 == 0
-                    and w.stride(1) == 1 and w.data_ptr() % 16 == 0)
+                    and w.stride(1) == 1 and w.data_ptr() % 16 == 0 and self.pre["part"].shape[1] == 16)
         return (self.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SKINNY_MAX_TOKENS
                 and K % 8 == 0 and K <= FUSED_NORM_MAX_K and w.stride(0) % 8 == 0 and w.stride(1) == 1
                 and w.data_ptr() % 16 == 0 and self.x.is_contiguous() and self.x.data_ptr() % 16 == 0)
@@ -355,6 +356,72 @@ def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE
         _remember(_norm_ready, out, dict(weight=ann[0], eps=ann[1], xw=emit_xw, part=emit_part, shape=(M, N)))
 
 
+_cluster_ctas: dict = {}
+
+
+def _cluster_plan(M: int, w_rows: int, K: int, epilogue: int) -> int:
+    """CTAs that the cluster product uses for these sizes; 0: it does not take them."""
+    key = (M, w_rows, K, epilogue)
+    n = _cluster_ctas.get(key)
+    if n is None:
+        lib = load_library("gemm_skinny")
+        n = _cluster_ctas[key] = int(lib.tuff_gemm_skinny_ctas(c_int(M), c_int(w_rows), c_int(K), c_int(epilogue)))
+    return n
+
+
+def _cluster_eligible(a, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> bool:
+    M = a.shape[0]
+    if not (SKINNY_MAX_TOKENS < M <= CLUSTER_MAX_TOKENS) or os.environ.get("TUFF_GEMM_CLUSTER", "1") == "0":
+        return False
+    if isinstance(a, NormedRows):
+        if a.dtype != torch.bfloat16:
+            return False
+        K, a_ok = a.shape[1], True
+    else:
+        K = a.shape[1]
+        a_ok = a.dtype == torch.bfloat16 and a.stride(1) == 1 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0
+    return (a_ok and w.dtype == torch.bfloat16 and K % 8 == 0 and w.stride(0) % 8 == 0 and w.stride(1) == 1
+            and w.data_ptr() % 16 == 0 and out.stride(1) == 1
+            and (out.dtype == torch.float32 if epilogue == EPI_ACCUM else out.dtype in (torch.bfloat16, torch.float32))
+            and _cluster_plan(M, w.shape[0], K, epilogue) > 0)
+
+
+def gemm_cluster(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:
+    """A product for 17 to 128 tokens with its neighbours fused in (csrc/gemm_skinny.cu): the K range of
+    every 128-column tile is split over a thread-block cluster and added in distributed shared memory.
+    `a` is a bf16 tensor [M, K] or a `NormedRows`; EPI_SWIGLU takes w = gate and up rows in blocks of 128."""
+    pre = None
+    if isinstance(a, NormedRows):
+        pre = a.pre
+        src = pre["xw"] if pre is not None else a.dense()
+    else:
+        src = a
+    M, K = src.shape
+    w_rows = w.shape[0]
+    n_out = w_rows // 2 if epilogue == EPI_SWIGLU else w_rows
+    assert w.shape[1] == K and out.shape == (M, n_out)
+    lib = load_library("gemm_skinny")
+    st = _tc_buffers(src.device, 0)
+    ann = _norm_announced.pop(out.data_ptr(), None) if (epilogue == EPI_ACCUM and _norm_announced) else None
+    _written(out)
+    emit_w = emit_xw = emit_part = None
+    if ann is not None and out.is_contiguous():
+        emit_w = ann[0]
+        emit_xw = torch.empty((M, n_out), dtype=torch.bfloat16, device=out.device)
+        emit_part = torch.empty((_cluster_plan(M, w_rows, K, epilogue), M), dtype=torch.float32, device=out.device)
+    part = pre["part"] if pre is not None else None
+    _check(lib.tuff_gemm_skinny(_ptr(src), _ptr(w), _ptr(out), dtype_code(out), c_int(M), c_int(w_rows), c_int(K),
+                                c_longlong(src.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
+                                c_int(epilogue), _ptr(emit_w), _ptr(emit_xw), _ptr(emit_part),
+                                c_int(emit_part.shape[1] if emit_part is not None else 0), _ptr(part),
+                                c_int(part.shape[0] if part is not None else 0),
+                                c_int(part.shape[1] if part is not None else 0),
+                                c_float(pre["eps"] if pre is not None else 0.0), _ptr(st["status"]), _stream()),
+           "gemm_skinny")
+    if emit_w is not None:
+        _remember(_norm_ready, out, dict(weight=ann[0], eps=ann[1], xw=emit_xw, part=emit_part, shape=(M, n_out)))
+
+
 def _decode_eligible(a, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
     if isinstance(a, NormedRows):
         return a.fusable(w) and out.stride(1) == 1 and (out.dtype == torch.float32 or not accumulate)
@@ -369,6 +436,9 @@ def linear_swiglu(a, w13: torch.Tensor, out: torch.Tensor, block: int = 0) -> No
     M, F = out.shape
     if out.dtype == torch.bfloat16 and _decode_eligible(a, w13, out, False):
         gemm_decode(a, w13, out, EPI_SWIGLU, set_block=block)
+        return
+    if block == 128 and out.dtype == torch.bfloat16 and _cluster_eligible(a, w13, out, EPI_SWIGLU):
+        gemm_cluster(a, w13, out, EPI_SWIGLU)
         return
     if isinstance(a, NormedRows):
         a = a.dense()
@@ -389,6 +459,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
     run): the decode product norms the rows itself, every other kernel gets the normed tensor."""
     if _decode_eligible(a, w, out, accumulate):
         gemm_decode(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
+        return
+    if _cluster_eligible(a, w, out, EPI_ACCUM if accumulate else EPI_STORE):
+        gemm_cluster(a, w, out, EPI_ACCUM if accumulate else EPI_STORE)
         return
     if isinstance(a, NormedRows):
         a = a.dense()

@@ -18,14 +18,14 @@ class RMSNorm(Norm):
         return {"weight": WeightDecl((self.dim,), role="vector", init="norm")}
 
     def announce(self, ctx, x):
-        # few rows in bf16: the decode product that adds into x last can prepare this norm
-        if x.shape[0] <= ops.SKINNY_MAX_TOKENS and self.act_dtype == torch.bfloat16:
+        # few rows in bf16: the product that adds into x last can prepare this norm
+        if x.shape[0] <= ops.CLUSTER_MAX_TOKENS and self.act_dtype == torch.bfloat16:
             ops.announce_norm(x, self.w["weight"], self.eps)
 
     def forward(self, ctx, x, row_index=None, lazy=False):
         """`lazy`: the caller's next step is a matrix product that can norm its own rows; it gets
         an `ops.NormedRows` (which any other consumer turns into the tensor with `.dense()`)."""
-        if lazy and row_index is None and x.shape[0] <= ops.SKINNY_MAX_TOKENS and self.act_dtype == torch.bfloat16:
+        if lazy and row_index is None and x.shape[0] <= ops.CLUSTER_MAX_TOKENS and self.act_dtype == torch.bfloat16:
             return ops.NormedRows(x, self.w["weight"], self.eps, self.act_dtype)
         n = x.shape[0] if row_index is None else row_index.numel()
         out = torch.empty((n, self.dim), dtype=self.act_dtype, device=x.device)
