@@ -93,6 +93,13 @@ __device__ __forceinline__ int ld_act(const int* p) { return __ldcg(p); }
 __device__ __forceinline__ uint32_t ld_act_u32(const void* p) { return __ldcg(reinterpret_cast<const unsigned int*>(p)); }
 __device__ __forceinline__ uint4 ld_act_u4(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
+// Nanoseconds of the GPU's global timer (for the kernels' optional time stamps).
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 static inline bool pdl_enabled() {
     static int on = -1;
     if (on < 0) {

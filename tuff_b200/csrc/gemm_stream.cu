@@ -1,4 +1,4 @@
-// The decode-step matrix products: C[M,N] = A[M,K] * W[N,K]^T for M <= 16 tokens, with what
+// The decode-step matrix products: C[M,N] = A[M,K] * W[N,K]^T for M <= 8 tokens, with what
 // surrounds them in a layer fused in, so that a layer is a few launches instead of a dozen.
 //
 // With so few tokens a product is a stream of W through the SMs; its time is the bytes of W over
@@ -33,8 +33,8 @@
 // multiplies its sums by rsqrt(mean square + eps) of the row in its epilogue ("row scale").  The
 // scale is a factor per token, so it commutes with the product; the sums of squares are added in
 // CTA order.
-// Up to 8 tokens the weights are the 16-row operand of the MMA and the tokens its 8 columns; with
-// 9..16 tokens the tokens are the 16 rows and the weights come in groups of 8 columns.
+// The weights are the 16-row operand of the MMA and the tokens its 8 columns.  (More tokens go to the
+// product that splits K over a thread-block cluster, gemm_skinny.cu: it is ahead from 9 tokens on.)
 //
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records a code in *status
 // (61 producer, 63 consumers), stops waiting, and runs to its end.
@@ -107,11 +107,6 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ long long global_ns() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -159,7 +154,7 @@ struct StageCursor {
     __device__ void next() { if (++st == spp) next_pass(); }
 };
 
-// MT: tokens the MMA tile holds (8 or 16); NORM: RMSNorm prologue; NGT: groups of 16 weight rows in a pass.
+// MT: tokens the MMA tile holds (8); NORM: RMSNorm prologue; NGT: groups of 16 weight rows in a pass.
 template <int MT, bool NORM, int NGT>
 __global__ void __launch_bounds__(THREADS, 2)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, StreamGemm p) {
@@ -363,7 +358,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
     // Two sets of accumulators (8 tokens; registers allow it): the K steps of an iteration alternate
     // between them, so an MMA does not wait for the one before it; the sets are added when a pass ends.
-    constexpr int NU = MT == 8 ? 2 : 1;
+    static_assert(MT == 8, "the tokens are the 8 columns of the MMA");
+    constexpr int NU = 2;
     // K steps of one iteration: all their fragments are loaded before the first MMA, and a warp's share
     // of a stage is one iteration where registers allow, because an iteration costs a fixed 200 clocks
     // (ldmatrix, then the MMA pipeline) on top of its MMAs
@@ -374,13 +370,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     int s = 0;
     uint32_t phase = 0, it = 0;
     const int rs = p.red_stride;
-    // This lane's part of the ldmatrix addresses.  Weights (and 16 tokens): row lane & 15 of a group, the
+    // This lane's part of the ldmatrix addresses.  Weights: row lane & 15 of a group, the
     // chunk pair lane >> 4; 8 tokens: row lane & 7, the chunk pair (lane >> 3) & 1.  Groups of 16 rows lie
     // 16 * jb lines apart, a multiple of 8, so all groups of a K step share one swizzle phase.
     const int w_line0 = (lane & 15) * jb, w_half = lane >> 4;
     const uint32_t w_group = (uint32_t)(2048 * jb);
     const int ja = NORM ? 1 : p.a_resident ? p.a_kb : jb;                // lines from one row of A to the next
-    const int a_line0 = (MT == 8 ? (lane & 7) : (lane & 15)) * ja, a_half = MT == 8 ? ((lane >> 3) & 1) : (lane >> 4);
+    const int a_line0 = (lane & 7) * ja, a_half = (lane >> 3) & 1;
     if (!NORM && p.a_resident && !mbar_test(a_full, 0)) ok = mbar_wait(a_full, 0, p.status, 63);
     for (; cur.valid(); cur.next_pass(), first_pass = false) {
         const int n_cols = cur.width();
@@ -398,7 +394,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // the normed rows lie as one 8- or 16-row tile per K block; the loaded ones as the weights do
             const uint32_t at = NORM ? a_region + (uint32_t)(kb0 * A_TILE) : p.a_resident ? a_region : a_region + (uint32_t)(s * a_stage);
             for (int step = warp; step < n_steps; step += US * CWARPS) {
-                uint32_t tf[US][4], wf[US][NGT][4];
+                uint32_t tf[US][2], wf[US][NGT][4];
 #pragma unroll
                 for (int u = 0; u < US; ++u) {
                     const int stp = min(step + u * CWARPS, n_steps - 1);         // past the end: loaded again, not used
@@ -406,8 +402,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     const int al = a_line0 + (NORM ? 0 : p.a_resident ? kb0 + q : q), wl = w_line0 + q;
                     const uint32_t aa = at + (NORM ? (uint32_t)(q * A_TILE) : 0u) + (uint32_t)(al * 128) + (uint32_t)(((2 * kk + a_half) ^ (al & 7)) << 4);
                     const uint32_t wa = wt + (uint32_t)(wl * 128) + (uint32_t)(((2 * kk + w_half) ^ (wl & 7)) << 4);
-                    if (MT == 8) ldsm_x2(aa, tf[u][0], tf[u][1]);
-                    else ldsm_x4(aa, tf[u][0], tf[u][1], tf[u][2], tf[u][3]);
+                    ldsm_x2(aa, tf[u][0], tf[u][1]);
 #pragma unroll
                     for (int i = 0; i < NGT; ++i) ldsm_x4(wa + (uint32_t)i * w_group, wf[u][i][0], wf[u][i][1], wf[u][i][2], wf[u][i][3]);
                 }
@@ -415,16 +410,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 for (int u = 0; u < US; ++u) {
                     if (step + u * CWARPS >= n_steps) break;
 #pragma unroll
-                    for (int i = 0; i < NGT; ++i) {
-                        if (MT == 8) {
-                            // 16 weight rows x 8 tokens
-                            mma16816(acc[u % NU][i][0], wf[u][i][0], wf[u][i][1], wf[u][i][2], wf[u][i][3], tf[u][0], tf[u][1]);
-                        } else {
-                            // 16 tokens x two groups of 8 weight rows
-                            mma16816(acc[0][i][0], tf[u][0], tf[u][1], tf[u][2], tf[u][3], wf[u][i][0], wf[u][i][2]);
-                            mma16816(acc[0][i][NH - 1], tf[u][0], tf[u][1], tf[u][2], tf[u][3], wf[u][i][1], wf[u][i][3]);
-                        }
-                    }
+                    for (int i = 0; i < NGT; ++i)          // 16 weight rows x 8 tokens
+                        mma16816(acc[u % NU][i][0], wf[u][i][0], wf[u][i][1], wf[u][i][2], wf[u][i][3], tf[u][0], tf[u][1]);
                 }
             }
             __syncwarp();
@@ -435,20 +422,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // ---- the pass is complete: add the warps' partial sums in warp order and write out
 #pragma unroll
         for (int i = 0; i < NGT; ++i) {
-            if (MT == 8) {
-                // acc[.][i][0][0..1]: weight row 16 i + g, tokens 2t, 2t+1;  [2..3]: weight row 16 i + g + 8
-                float* r = red + (size_t)(warp * MT + 2 * t) * rs + i * 16 + g;
-                r[0] = acc[0][i][0][0] + acc[NU - 1][i][0][0]; r[rs] = acc[0][i][0][1] + acc[NU - 1][i][0][1];
-                r[8] = acc[0][i][0][2] + acc[NU - 1][i][0][2]; r[rs + 8] = acc[0][i][0][3] + acc[NU - 1][i][0][3];
-            } else {
-#pragma unroll
-                for (int h = 0; h < NH; ++h) {
-                    // acc[0][i][h][0..1]: token g, weight rows 16 i + 8 h + 2t, +1;  [2..3]: token g + 8
-                    float* r = red + (size_t)(warp * MT + g) * rs + i * 16 + h * 8 + 2 * t;
-                    r[0] = acc[0][i][h][0]; r[1] = acc[0][i][h][1];
-                    r[(size_t)8 * rs] = acc[0][i][h][2]; r[(size_t)8 * rs + 1] = acc[0][i][h][3];
-                }
-            }
+            // acc[.][i][0][0..1]: weight row 16 i + g, tokens 2t, 2t+1;  [2..3]: weight row 16 i + g + 8
+            float* r = red + (size_t)(warp * MT + 2 * t) * rs + i * 16 + g;
+            r[0] = acc[0][i][0][0] + acc[NU - 1][i][0][0]; r[rs] = acc[0][i][0][1] + acc[NU - 1][i][0][1];
+            r[8] = acc[0][i][0][2] + acc[NU - 1][i][0][2]; r[rs + 8] = acc[0][i][0][3] + acc[NU - 1][i][0][3];
         }
         if (first_pass && p.scale_part) {
 #pragma unroll
@@ -634,7 +611,7 @@ extern "C" int tuff_gemm_stream_grid(int N) { return N > 0 ? stream_grid(N) : 0;
 // short convolution (W is [3N, K]: B, C, x rows; one token per row of A; taps [N, L], state
 // [slots, L-1, N], slot_of_row [M]).  norm_w: if not null, A is the fp32 residual [M, K] and is
 // RMS-normed with this weight and eps first; else A is bf16 [M, K].
-// Requirements: M <= 16, K % 8 == 0, ldw % 8 == 0, 16-byte aligned bases; bf16 A: lda % 8 == 0;
+// Requirements: M <= 8, K % 8 == 0, ldw % 8 == 0, 16-byte aligned bases; bf16 A: lda % 8 == 0;
 // fp32 A: lda % 4 == 0 and K <= 2048.  C is bf16 or fp32 (fp32 only for epilogue 1).
 // set_block: for epilogues 2 and 3, how the row sets lie in W: 0 = stacked whole ([gate; up]), else
 // blocks of that many rows of each set in turn (N a multiple of it).
@@ -651,7 +628,7 @@ extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, c
                                 const float* scale_part, int scale_parts, float scale_eps,
                                 int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 16 || K <= 0 || epilogue < 0 || epilogue > 3 || !status) return TUFF_E_SIZE;
+    if (M > 8 || K <= 0 || epilogue < 0 || epilogue > 3 || !status) return TUFF_E_SIZE;
     if ((K % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TUFF_E_ALIGN;
     if (norm_w ? (lda % 4 != 0 || ((uintptr_t)norm_w & 15)) : (lda % 8 != 0)) return TUFF_E_ALIGN;
     if (epilogue == EPI_ACCUM && c_dtype != TUFF_F32) return TUFF_E_DTYPE;
@@ -663,7 +640,7 @@ extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, c
     if (emit_w && (epilogue != EPI_ACCUM || !emit_xw || !emit_part)) return TUFF_E_SIZE;
     if (scale_part && (norm_w || scale_parts <= 0 || scale_parts > 256)) return TUFF_E_SIZE;
     const bool norm = norm_w != nullptr;
-    const int MT = M <= 8 ? 8 : 16;
+    constexpr int MT = 8;
     StreamGemm p{};
     p.a = A; p.norm_w = norm_w; p.out = C; p.status = status; p.lda = lda; p.ldc = ldc;
     p.M = M; p.N = N; p.K = K; p.eps = eps; p.epi = epilogue; p.out_dtype = c_dtype;
@@ -717,8 +694,7 @@ extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, c
     else if (!stream_map(&ma, A, K, M, 1, 1, lda, p.a_resident ? p.a_kb : p.kb_per_stage, MT, 1)) return TUFF_E_ALIGN;
     const int ngt = p.tile_rows / 16;
 #define TUFF_PICK(NGV)                                                                                         \
-    (MT == 8 ? (norm ? launch<8, true, NGV>(mw, ma, p, grid, smem, stream) : launch<8, false, NGV>(mw, ma, p, grid, smem, stream)) \
-             : (norm ? launch<16, true, NGV>(mw, ma, p, grid, smem, stream) : launch<16, false, NGV>(mw, ma, p, grid, smem, stream)))
+    (norm ? launch<8, true, NGV>(mw, ma, p, grid, smem, stream) : launch<8, false, NGV>(mw, ma, p, grid, smem, stream))
     const int rc = ngt == 1 ? TUFF_PICK(1) : ngt == 2 ? TUFF_PICK(2) : ngt == 3 ? TUFF_PICK(3) : TUFF_PICK(4);
 #undef TUFF_PICK
     return rc;

@@ -34,7 +34,8 @@ CHECKED_LIBS = ("attention_plain", "attention_flash", "attention_tc", "shortconv
 
 def _flags(name: str) -> list[str]:
     extra = ["-DTUFF_DEBUG_BOUNDS"] if name in CHECKED_LIBS and os.environ.get("TUFF_DEBUG_BOUNDS", "0") not in ("", "0") else []
-    return NVCC_FLAGS + extra
+    # TUFF_NVCC_EXTRA: further flags (-D...) for experiments with a kernel's compile-time choices
+    return NVCC_FLAGS + extra + os.environ.get("TUFF_NVCC_EXTRA", "").split()
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -237,8 +237,11 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
                             _ptr(st["status"]), _stream()), "gemm_tc")
 
 
-SKINNY_MAX_TOKENS = 16           # the decode product on mma.sync (csrc/gemm_stream.cu)
-CLUSTER_MAX_TOKENS = 128         # the product that splits K over a cluster (csrc/gemm_skinny.cu)
+# The decode product on mma.sync (csrc/gemm_stream.cu) takes up to 8 tokens: measured against the cluster product
+# it is ahead up to there (0.74 against 0.76 ms a step at 8 rows) and behind beyond (0.94 against 0.77 ms at 12).
+# TUFF_STREAM_MAX_TOKENS gives it fewer (0: none).
+SKINNY_MAX_TOKENS = max(0, min(8, int(os.environ.get("TUFF_STREAM_MAX_TOKENS", "8"))))
+CLUSTER_MAX_TOKENS = 128         # the product that splits K over a cluster (csrc/gemm_skinny.cu): from there up to 128 tokens
 FUSED_NORM_MAX_K = 2048          # the widest row the fused RMSNorm of a decode product holds in registers
 
 
@@ -314,7 +317,7 @@ EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_CONV = 0, 1, 2, 3
 
 
 def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, conv=None, set_block: int = 0) -> None:
-    """A decode-step product for at most 16 tokens with its neighbours fused in (csrc/gemm_stream.cu):
+    """A decode-step product for at most 8 tokens with its neighbours fused in (csrc/gemm_stream.cu):
     `a` is a bf16 tensor [M, K] or a `NormedRows`; epilogue EPI_SWIGLU takes w = [gate; up] stacked,
     EPI_CONV takes w = [B; C; x] stacked and conv = (taps [d, L], state [slots, L-1, d], slot_of_row)."""
     norm = a if isinstance(a, NormedRows) else None
@@ -387,7 +390,7 @@ def _cluster_eligible(a, w: torch.Tensor, out: torch.Tensor, epilogue: int) -> b
 
 
 def gemm_cluster(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:
-    """A product for 17 to 128 tokens with its neighbours fused in (csrc/gemm_skinny.cu): the K range of
+    """A product for 9 to 128 tokens with its neighbours fused in (csrc/gemm_skinny.cu): the K range of
     every 128-column tile is split over a thread-block cluster and added in distributed shared memory.
     `a` is a bf16 tensor [M, K] or a `NormedRows`; EPI_SWIGLU takes w = gate and up rows in blocks of 128."""
     pre = None
