@@ -3,6 +3,7 @@ throughput, and a small program to put under a profiler.
 
     python -m tuff_b200.kernels.probe gemm_tc --m 2048 --n 11264 --k 2048
     python -m tuff_b200.kernels.probe gemm_decode --m 8 --n 5632 --k 2048 --epilogue swiglu --norm
+    python -m tuff_b200.kernels.probe gemm_cluster --m 64 --n 2048 --k 5632 --epilogue accum
     python -m tuff_b200.kernels.probe decode_chain --m 8 --layers 16
     python -m tuff_b200.kernels.probe attention_decode --batch 8 --context 8192
     python -m tuff_b200.kernels.probe attention_prefill --tokens 2048
@@ -10,12 +11,16 @@ throughput, and a small program to put under a profiler.
     python -m tuff_b200.kernels.probe decode_step --config C.json --batch 8 --context 8192 --steps 6 --no-graphs
     python -m tuff_b200.kernels.probe prefill_step --config C.json --tokens 2048 --steps 3
     python -m tuff_b200.kernels.probe mixed_step --config C.json --batch 32 --context 4096 --tokens 512 --steps 5
+    python -m tuff_b200.kernels.probe product_phases --config C.json --batch 64 --context 256
 
 Timing: CUDA events around each launch, after warm-up, with a buffer larger than L2 written
 between launches.  Prints the median time and the achieved rate against the bytes or flops the
 kernel has to move or do.  The `*_step` forms run whole steps of the engine on a random-weights
 model of the sizes in the given config.json (contexts filled without computing them) and print the
-wall time a step; under a profiler they give the list of a step's launches.
+wall time a step; under a profiler they give the list of a step's launches.  `product_phases` runs one
+decode step (a CUDA graph replay) with the decode products' own time stamps switched on and prints, per
+product, when its CTAs started, when they were allowed to read activations, when their first weights
+had arrived, when the sums were complete and when the result was written.
 """
 from __future__ import annotations
 
@@ -63,6 +68,8 @@ def run_steps(a) -> int:
     from ..sampling import SamplingParams
     rng = np.random.default_rng(0)
     vocab = shape["vocab_size"]
+    if a.kernel == "product_phases":
+        return product_phases(a, shape)
     if a.kernel == "decode_step":
         n_new = a.steps + 8
         eng = Engine(None, dtype="bfloat16", ctx_size=a.context, max_tokens=a.batch * a.context + 4096, page_size=a.page_size,
@@ -124,10 +131,67 @@ def run_steps(a) -> int:
     return 0
 
 
+def product_phases(a, shape) -> int:
+    """One decode step with the products' time stamps on (tuff_gemm_stream_trace up to 8 rows,
+    tuff_gemm_skinny_trace beyond): medians over a product's CTAs, microseconds from the CTAs' first start."""
+    import ctypes
+
+    import numpy as np
+
+    from ..engine.engine import Engine
+    from ..engine.scheduler import RequestStatus
+    from ..sampling import SamplingParams
+    from .build import load_library
+    rng = np.random.default_rng(0)
+    n_new = 40
+    eng = Engine(None, dtype="bfloat16", ctx_size=a.context, max_tokens=a.batch * a.context + 4096, page_size=a.page_size,
+                 max_running=a.batch, config=dict(shape), cuda_graphs=True, run_ahead=False)
+    for i in range(a.batch):
+        r = eng.scheduler.add(i, rng.integers(0, shape["vocab_size"], a.context - n_new).tolist(), SamplingParams(max_new_tokens=n_new))
+        eng.scheduler.waiting.remove(r)
+        r.cache = eng.runner.open(i)
+        eng.runner.synthetic_fill(r.cache, a.context - n_new - 1)
+        r.status = RequestStatus.RUNNING
+        eng.scheduler.running.append(r)
+    stream_kernel = a.batch <= ops.SKINNY_MAX_TOKENS
+    lib = load_library("gemm_stream" if stream_kernel else "gemm_skinny")
+    set_trace = lib.tuff_gemm_stream_trace if stream_kernel else lib.tuff_gemm_skinny_trace
+    n = 256
+    buf = torch.zeros(n * 256 * 8, dtype=torch.int64, device="cuda")
+    eng.step()                                                    # the last prompt tokens, plain launches
+    set_trace(ctypes.c_void_p(buf.data_ptr()), ctypes.c_int(n))
+    eng.step()                                                    # captured with the stamps on, and replayed once
+    set_trace(ctypes.c_void_p(0), ctypes.c_int(0))
+    torch.cuda.synchronize()
+    t = buf.cpu().numpy().reshape(n, 256, 8).astype(np.float64)
+    # stamps: the stream kernel 0 start, 6 ring filled, 1 predecessor done, 2 activations ready, 3 first stage, 4 sums, 5 written;
+    # the cluster kernel 0 start, 1 set up, 2 predecessor done, 3 first stage, 4 sums, 5 rows exchanged, 6 written
+    cols = ([("primed", 6), ("pred.done", 1), ("acts", 2), ("1st stage", 3), ("sums", 4), ("written", 5)] if stream_kernel else
+            [("set up", 1), ("pred.done", 2), ("1st stage", 3), ("sums", 4), ("exchanged", 5), ("written", 6)])
+    print(f"product_phases batch={a.batch} context={a.context}: us after the product's first CTA started (medians over CTAs)")
+    print("  #  CTAs   start  " + "".join(f"{c:>10s}" for c, _ in cols) + "       end   since prev. end")
+    t0 = prev = None
+    for i in range(n):
+        m = t[i][:, 0] > 0
+        if not m.any():
+            break
+        r = t[i][m]
+        if t0 is None:
+            t0 = r[:, 0].min()
+        r = (r - t0) / 1e3
+        st = r[:, 0].min()
+        last = cols[-1][1]
+        end = r[:, last].max()
+        print(f"{i:3d} {int(m.sum()):5d} {st:8.2f}  " + "".join(f"{np.median(r[:, k]) - st:10.2f}" for _, k in cols) +
+              f" {end:9.2f} {'' if prev is None else f'{end - prev:9.2f}'}")
+        prev = end
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_decode", "decode_chain", "attention_decode", "attention_prefill",
-                                       "decode_step", "prefill_step", "mixed_step"])
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_decode", "gemm_cluster", "decode_chain", "attention_decode", "attention_prefill",
+                                       "decode_step", "prefill_step", "mixed_step", "product_phases"])
     ap.add_argument("--config", help="*_step: a config.json with the sizes of the model")
     ap.add_argument("--layers", type=int, default=16, help="decode_chain: layers of four products each")
     ap.add_argument("--ffn", type=int, default=5632, help="decode_chain: width of the feed-forward")
@@ -151,7 +215,7 @@ def main(argv=None) -> int:
     torch.manual_seed(0)
     dev = "cuda"
     bf = torch.bfloat16
-    if a.kernel.endswith("_step"):
+    if a.kernel.endswith("_step") or a.kernel == "product_phases":
         return run_steps(a)
 
     if a.kernel == "gemm_tc":
@@ -188,6 +252,19 @@ def main(argv=None) -> int:
         nbytes = mult * a.n * a.k * 2
         print(f"gemm_decode m={a.m} n={a.n} k={a.k} {a.epilogue}{' +norm' if a.norm else ''}: {t * 1e6:.1f} us, "
               f"{nbytes / t / 1e9:.0f} GB/s of weights ({nbytes / 1e6:.1f} MB)")
+    elif a.kernel == "gemm_cluster":
+        epi = {"store": ops.EPI_STORE, "accum": ops.EPI_ACCUM, "swiglu": ops.EPI_SWIGLU}[a.epilogue]
+        mult = 2 if a.epilogue == "swiglu" else 1
+        w = (torch.randn(mult * a.n, a.k, device=dev) * 0.02).to(bf)
+        x = torch.randn(a.m, a.k, device=dev).to(bf)
+        out = torch.zeros(a.m, a.n, dtype=torch.float32 if a.epilogue == "accum" else bf, device=dev)
+        if not ops._cluster_eligible(x, w, out, epi):
+            print("gemm_cluster: the cluster product does not take these sizes", file=sys.stderr)
+            return 2
+        t = timed(lambda: ops.gemm_cluster(x, w, out, epi), a.reps)
+        nbytes = mult * a.n * a.k * 2
+        print(f"gemm_cluster m={a.m} n={a.n} k={a.k} {a.epilogue}: {t * 1e6:.1f} us, "
+              f"{nbytes / t / 1e9:.0f} GB/s of weights ({nbytes / 1e6:.1f} MB), {ops._cluster_plan(a.m, mult * a.n, a.k, epi)} CTAs")
     elif a.kernel == "decode_chain":
         # The products of `layers` short-convolution layers back to back, each with weights of its own
         # (nothing is found in L2 again), replayed from one CUDA graph: what the decode step's products
