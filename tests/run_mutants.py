@@ -21,6 +21,17 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CPU_TESTS = ("tests/test_scheduler.py", "tests/test_cache_manager.py", "tests/test_config_weights.py", "tests/test_plain.py", "tests/test_index_helpers.py")
 
 
+def untracked_patterns():
+    """What .gitignore lists (built files, caches, scratch folders): none of it belongs in the scratch copy."""
+    out = []
+    with open(os.path.join(ROOT, ".gitignore")) as f:
+        for line in f:
+            line = line.strip()
+            if line and not line.startswith("#"):
+                out.append(line.strip("/").split("/")[0])
+    return out
+
+
 def read_mutants(path):
     out, cur = [], None
     with open(path) as f:
@@ -64,8 +75,7 @@ def main():
         mutants = [m for m in mutants if m["test"].split("::")[0] in CPU_TESTS]
     scratch = tempfile.mkdtemp(prefix="tuff_mutants_")
     copy = os.path.join(scratch, "repo")
-    shutil.copytree(ROOT, copy, ignore=shutil.ignore_patterns(".git", "_work", "gpurun_out", "_build", "__pycache__", "baseline",
-                                                              ".pytest_cache", "*.ncu-rep"))
+    shutil.copytree(ROOT, copy, ignore=shutil.ignore_patterns(".git", *untracked_patterns()))
     bad = 0
     try:
         # the baseline: every named test passes on the unchanged copy
