@@ -33,8 +33,11 @@ import torch
 from . import ops
 
 
+FLUSH_L2 = [True]      # --warm-l2: leave what a launch read in L2 for the next one
+
+
 def timed(fn, reps: int, warmup: int = 3):
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    flush = torch.empty(256 * 1024 * 1024 if FLUSH_L2[0] else 16, dtype=torch.uint8, device="cuda")
     for _ in range(warmup):
         fn()
     times = []
@@ -210,8 +213,10 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--warm-l2", action="store_true", help="do not flush L2 between timed launches")
     ap.add_argument("--shuffle-pages", action="store_true", help="attention: a request's pages lie scattered over the pool")
     a = ap.parse_args(argv)
+    FLUSH_L2[0] = not a.warm_l2
     torch.manual_seed(0)
     dev = "cuda"
     bf = torch.bfloat16
