@@ -594,3 +594,145 @@ def test_layers_with_windows_have_pages_of_their_own(tmp_path, dtype):
     assert held["None"] == 19 and held["40"] <= 6 and held["24"] <= 4        # 150 tokens in pages of 8; windows keep a few
     runner.close(rcs["a"]); runner.close(rcs["b"])
     cm.check()
+
+
+# ---- state whose neutral element is not zero; values wider than keys ---------------------------
+def register_toy_max_and_wide_values():
+    """Two more mixers defined here and nowhere in the package: a running maximum per channel (its
+    state starts at the lowest float, `StateNeed(fill=...)`), and single-head attention whose values are
+    three times as wide as its keys (`PagedKVNeed(v_head_dim=...)`), written to and read from the pages
+    on the host's say."""
+    from tuff_b200.parts import MIXERS, Mixer, PagedKVNeed, StateNeed, WeightDecl, register_mixer
+    if "toy_running_max" in MIXERS.kinds():
+        return
+
+    @register_mixer("toy_running_max")
+    class ToyMax(Mixer):
+        replayable = False
+
+        def __init__(self, d_model):
+            self.d = d_model
+
+        def weight_decls(self):
+            return {"proj": WeightDecl((self.d, self.d))}
+
+        def cache_need(self):
+            return StateNeed(shape=(self.d,), dtype="float32", fill=LOWEST)
+
+        def forward(self, ctx, cache, h, residual, reads_only=False):
+            cu, slots = ctx.host["cu_q"], ctx.host["slot_of_row"]
+            y = torch.empty_like(h, dtype=torch.float32)
+            for r in range(ctx.n_rows):
+                s = cache.state[int(slots[r])]
+                for t in range(int(cu[r]), int(cu[r + 1])):
+                    s = torch.maximum(s, h[t].float())
+                    y[t] = s
+                cache.state[int(slots[r])] = s
+            residual += (y.to(h.dtype) @ self.w["proj"].T).float()
+
+    @register_mixer("toy_wide_values")
+    class ToyWideValues(Mixer):
+        replayable = False
+
+        def __init__(self, d_model, key_dim, value_dim):
+            self.d, self.dk, self.dv = d_model, key_dim, value_dim
+
+        def weight_decls(self):
+            return {"q": WeightDecl((self.dk, self.d)), "k": WeightDecl((self.dk, self.d)),
+                    "v": WeightDecl((self.dv, self.d)), "o": WeightDecl((self.d, self.dv))}
+
+        def cache_need(self):
+            return PagedKVNeed(kv_heads=1, head_dim=self.dk, v_head_dim=self.dv)
+
+        def forward(self, ctx, cache, h, residual, reads_only=False):
+            q, k, v = (h @ self.w[n].T for n in "qkv")
+            table = ctx.host["block_tables"][cache.group]
+            cu, pos, page = ctx.host["cu_q"], ctx.host["positions"], cache.page_size
+            out = torch.empty((h.shape[0], self.dv), dtype=h.dtype, device=h.device)
+            for r in range(ctx.n_rows):
+                for t in range(int(cu[r]), int(cu[r + 1])):
+                    p = int(pos[t])
+                    cache.k_pages[int(table[r][p // page]), 0, p % page] = k[t]
+                    cache.v_pages[int(table[r][p // page]), 0, p % page] = v[t]
+                    keys = torch.stack([cache.k_pages[int(table[r][j // page]), 0, j % page] for j in range(p + 1)])
+                    vals = torch.stack([cache.v_pages[int(table[r][j // page]), 0, j % page] for j in range(p + 1)])
+                    w = torch.softmax((keys.float() @ q[t].float()) / math.sqrt(self.dk), 0)
+                    out[t] = (w @ vals.float()).to(h.dtype)
+            residual += (out @ self.w["o"].T).float()
+
+
+LOWEST = float(np.finfo(np.float32).min)
+
+
+def test_state_with_its_own_neutral_element_and_values_wider_than_keys(tmp_path):
+    """What another architecture might bring without a change to the cache manager: a state that does not
+    start at zero, and pages whose values have another width than their keys.  Stepped in portions of
+    changing size, two requests at once, a slot and pages used again; against a plain restatement."""
+    from tuff_b200.config import Architecture, register_architecture
+    from tuff_b200.engine import ModelRunner
+    from tuff_b200.models import LayerSpec, ModelSpec
+    from tuff_b200.parts import PartSpec
+    from tuff_b200.weights import write_random_model
+    register_toy_max_and_wide_values()
+    d, V, F, dk, dv = 40, 61, 48, 8, 24
+
+    def spec(cfg):
+        layers = []
+        for i, kind in enumerate(("max", "wide")):
+            p = f"l{i}."
+            mixer = (PartSpec("toy_running_max", dict(d_model=d), {"proj": p + "proj"}) if kind == "max" else
+                     PartSpec("toy_wide_values", dict(d_model=d, key_dim=dk, value_dim=dv), {n: p + n for n in "qkvo"}))
+            layers.append(LayerSpec(mixer=mixer, ffn=PartSpec("swiglu", dict(d_model=d, ffn_dim=F), {n: p + n for n in ("w1", "w2", "w3")}),
+                                    mixer_norm=PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": p + "n1"}),
+                                    ffn_norm=PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": p + "n2"})))
+        return ModelSpec("ToyMaxLM", d, V, PartSpec("token_embedding", dict(vocab_size=V, d_model=d), {"weight": "emb"}),
+                         layers, PartSpec("rmsnorm", dict(dim=d, eps=1e-5), {"weight": "nf"}),
+                         PartSpec("lm_head", dict(vocab_size=V, d_model=d), {"weight": "emb"}))
+
+    register_architecture(Architecture("ToyMaxLM", lambda raw, where: raw, spec, lambda c: dict(c)))
+    folder = write_random_model(str(tmp_path / "toymax"), dict(architectures=["ToyMaxLM"]), 9, store_dtype=torch.float32)
+    runner = ModelRunner(folder, dtype="float32", max_tokens=48, page_size=4, max_requests=2)
+    paged = [s for s in runner.cache.storages if type(s).__name__ == "PagedStorage"][0]
+    assert paged.k_pages.shape[-1] == dk and paged.v_pages.shape[-1] == dv
+    w = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+
+    def reference(tokens):
+        x = w["emb"][tokens]
+        h = plain.rms_norm(x, w["l0.n1"], 1e-5)
+        x = x + np.maximum.accumulate(h, axis=0) @ w["l0.proj"].T
+        x = x + plain.swiglu_ffn(plain.rms_norm(x, w["l0.n2"], 1e-5), w["l0.w1"], w["l0.w3"], w["l0.w2"])
+        h = plain.rms_norm(x, w["l1.n1"], 1e-5)
+        q, k, v = h @ w["l1.q"].T, h @ w["l1.k"].T, h @ w["l1.v"].T
+        s = q @ k.T / math.sqrt(dk)
+        s = np.where(np.triu(np.ones_like(s, dtype=bool), 1), -np.inf, s)
+        p = np.exp(s - s.max(-1, keepdims=True))
+        x = x + (p / p.sum(-1, keepdims=True)) @ v @ w["l1.o"].T
+        x = x + plain.swiglu_ffn(plain.rms_norm(x, w["l1.n2"], 1e-5), w["l1.w1"], w["l1.w3"], w["l1.w2"])
+        return plain.lm_head(x, w["nf"], 1e-5, w["emb"])
+
+    rng = np.random.default_rng(4)
+    seqs = {"a": rng.integers(0, V, 17).tolist(), "b": rng.integers(0, V, 9).tolist()}
+    refs = {k: reference(v) for k, v in seqs.items()}
+    rcs = {k: runner.open(k) for k in seqs}
+    pos = {k: 0 for k in seqs}
+    cuts = {"a": [3, 1, 6, 2, 5], "b": [2, 1, 1, 5]}
+    while any(pos[k] < len(seqs[k]) for k in seqs):
+        entries, keys = [], []
+        for k in seqs:
+            if pos[k] < len(seqs[k]):
+                n = cuts[k].pop(0)
+                entries.append(StepEntry(rcs[k], seqs[k][pos[k]:pos[k] + n], list(range(n))))
+                keys.append((k, n))
+        logits = f64(runner.step(entries))
+        o = 0
+        for k, n in keys:
+            np.testing.assert_allclose(logits[o:o + n], refs[k][pos[k]:pos[k] + n], atol=2e-4, rtol=2e-4)
+            pos[k] += n
+            o += n
+    # the slot and the pages of a finished request, taken again: the state starts at its own neutral element
+    runner.close(rcs["a"])
+    rc = runner.open("again")
+    logits = f64(runner.step([StepEntry(rc, seqs["b"], [len(seqs["b"]) - 1])]))
+    np.testing.assert_allclose(logits[0], refs["b"][-1], atol=2e-4, rtol=2e-4)
+    runner.close(rc); runner.close(rcs["b"])
+    runner.cache.check()

@@ -9,7 +9,7 @@ Storages and groups.  The model says, per cache storage, what it needs
 (`PagedKVNeed` or `StateNeed`, or nothing).  Paged storages with the same
 (kv_heads, head_dim, window) form a *group*: one page pool, one block table per
 request, and a K and a V tensor `[num_pages, kv_heads, page_size, head_dim]` per
-storage, all indexed by the group's page ids.  Groups with different needs (all
+storage (V with `v_head_dim` where a need gives one), all indexed by the group's page ids.  Groups with different needs (all
 keys / a window of keys, other head shapes) have pools and tables of their own.
 State storages share one slot pool: a request holds one slot number, and each
 storage has a tensor `[num_slots, *shape]`.
@@ -49,6 +49,7 @@ class StateStorage:
     """What a layer with fixed-size state sees: `state[slot]` is a request's state."""
     shape: Tuple[int, ...]
     state: torch.Tensor | None = None
+    fill: float = 0.0            # what a request's state holds when the request gets its slot
 
 
 @dataclass
@@ -111,14 +112,14 @@ class CacheManager:
                 if device is not None:
                     shape = (self.num_pages, need.kv_heads, self.page_size, need.head_dim)
                     st.k_pages = torch.empty(shape, dtype=dtype, device=device)
-                    st.v_pages = torch.empty(shape, dtype=dtype, device=device)
+                    st.v_pages = torch.empty(shape[:3] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
                 self.storages.append(st)
             elif isinstance(need, StateNeed):
                 self.has_state = True
-                st = StateStorage(tuple(need.shape))
+                st = StateStorage(tuple(need.shape), fill=float(need.fill))
                 if device is not None:
-                    st.state = torch.zeros((self.max_requests,) + tuple(need.shape),
-                                           dtype=getattr(torch, need.dtype), device=device)
+                    st.state = torch.full((self.max_requests,) + tuple(need.shape), float(need.fill),
+                                          dtype=getattr(torch, need.dtype), device=device)
                 self.storages.append(st)
             else:
                 raise TypeError(f"storage {i}: unknown cache need {need!r}")
@@ -132,7 +133,7 @@ class CacheManager:
         if self.device is not None:
             for st in self.storages:
                 if isinstance(st, StateStorage):
-                    st.state[slot].zero_()
+                    st.state[slot].fill_(st.fill)
         self.live[request_id] = rc
         return rc
 

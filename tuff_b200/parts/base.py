@@ -49,17 +49,21 @@ class WeightDecl:
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values that grow with the tokens; `window` = how many of the
-    latest keys a token may see (None: all of them)."""
+    latest keys a token may see (None: all of them).  `v_head_dim`: the width of a value where it
+    differs from a key's (the pages of V are then `[pages, kv_heads, page_size, v_head_dim]`)."""
     kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
 
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Per-request state of fixed size, zeroed when a request gets its slot."""
+    """Per-request state of fixed size, set to `fill` (the state's neutral element; zero for sums)
+    when a request gets its slot."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+    fill: float = 0.0
 
 
 @dataclass
