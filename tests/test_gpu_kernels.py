@@ -532,7 +532,8 @@ def test_linear_swiglu_blocked_layout(dtype, M, F, K):
 
 # ---- the product of 17 to 128 tokens: K split over a thread-block cluster, sums met in distributed shared memory
 @pytest.mark.parametrize("M,N,K", [(17, 2048, 2048), (64, 2048, 5632), (33, 384, 200), (128, 6144, 2048), (100, 520, 1000),
-                                   (40, 130, 264), (64, 2048, 8192), (96, 3072, 2048), (20, 128, 64)])
+                                   (40, 130, 264), (64, 2048, 8192), (96, 3072, 2048), (20, 128, 64), (9, 2048, 2048),
+                                   (16, 6144, 2048), (12, 264, 96)])
 def test_gemm_cluster_store_and_accumulate(M, N, K):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(31)
@@ -560,7 +561,7 @@ def test_gemm_cluster_store_and_accumulate(M, N, K):
     ops.check_tc_status()
 
 
-@pytest.mark.parametrize("M,F,K", [(17, 256, 96), (64, 5632, 2048), (128, 8192, 2048), (50, 1280, 264)])
+@pytest.mark.parametrize("M,F,K", [(17, 256, 96), (64, 5632, 2048), (128, 8192, 2048), (50, 1280, 264), (9, 5632, 2048), (16, 8192, 2048)])
 def test_gemm_cluster_swiglu(M, F, K):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(32)
@@ -578,7 +579,8 @@ def test_gemm_cluster_swiglu(M, F, K):
     ops.check_tc_status()
 
 
-@pytest.mark.parametrize("M,d,K,F", [(64, 2048, 2048, 5632), (17, 264, 96, 256), (128, 2048, 5632, 1024), (37, 1000, 80, 384)])
+@pytest.mark.parametrize("M,d,K,F", [(64, 2048, 2048, 5632), (17, 264, 96, 256), (128, 2048, 5632, 1024), (37, 1000, 80, 384),
+                                     (9, 2048, 8192, 256), (16, 264, 96, 128)])
 def test_gemm_cluster_norm_split_over_two_products(M, d, K, F):
     """The product that adds into the residual prepares the RMSNorm that follows (bf16(x * w), sums of squares per
     CTA and token); the products that consume the norm scale their tokens' results: against fp64."""
