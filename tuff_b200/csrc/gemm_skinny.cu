@@ -173,6 +173,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
     if (trace && threadIdx.x == 0) trace[1] = global_ns();
+    // A store into a peer's shared memory needs the peer to have started.  Every thread arrives here, and waits
+    // (long after, so never in earnest) before the first such store.
+    cluster_arrive();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -242,6 +245,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const uint32_t dst0 = peer_addr(recv, owner) + (uint32_t)((rank * BN * o_rows + (row - share_lo(owner, S) * 4)) * 4);
         if (!mbar_wait(acc_full, 0, p.status, 53)) ok = false;
         ok = __all_sync(0xffffffffu, ok);                      // tcgen05.ld below is a warp-wide instruction
+        cluster_wait();                                        // every CTA of the cluster runs (see above)
         if (trace && t == 0) trace[4] = global_ns();
         tc_fence_after();
         constexpr int CH = SKINNY_CH < BN ? SKINNY_CH : BN;    // columns read from tensor memory at a time
@@ -266,6 +270,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         tc_fence_before();
     }
     __syncwarp();
+    if (warp < 2) cluster_wait();                              // the first phase of the cluster barrier, for these warps
     cluster_arrive();
     // ---- part two (all warps): this CTA's share of the tile's rows, added over the slots in CTA order
     const int t2 = threadIdx.x;
