@@ -174,6 +174,9 @@ __device__ __forceinline__ void load_tile(const CUtensorMap* mk, const CUtensorM
 // ------------------------------------------------------------------ decode
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_STAGES = 4;
+// Warp w takes tiles w, w + DEC_WARPS, ...: with as many stages as warps a stage always belongs to the same warp,
+// which therefore never waits for a phase of its barrier two ahead of the one it last saw.
+static_assert(DEC_STAGES == DEC_WARPS, "a stage must always be read by the same warp");
 
 template <int HD>
 __global__ void __launch_bounds__((DEC_WARPS + 1) * 32)
