@@ -56,7 +56,8 @@ def test_rmsnorm(dtype, d, n, eps):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K", [(1, 301, 80), (7, 130, 200), (65, 64, 48), (130, 257, 1000), (3, 2048, 5632),
-                                   (300, 520, 136), (512, 2048, 192), (257, 129, 72), (1100, 777, 2048), (2048, 3080, 136)])
+                                   (300, 520, 136), (512, 2048, 192), (257, 129, 72), (1100, 777, 2048), (2048, 3080, 136),
+                                   (260, 2048, 8192), (40, 2048, 8192)])
 def test_linear(dtype, M, N, K):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(2)
@@ -462,7 +463,7 @@ def test_gemm_decode_norm_split_over_two_products(M, d, K, N2):
     ops.check_tc_status()
 
 
-@pytest.mark.parametrize("M,F,K", [(1, 100, 80), (8, 5632, 2048), (8, 264, 96), (7, 40, 64)])
+@pytest.mark.parametrize("M,F,K", [(1, 100, 80), (8, 5632, 2048), (8, 264, 96), (7, 40, 64), (4, 8192, 2048)])
 def test_gemm_decode_swiglu(M, F, K):
     from tuff_b200.kernels import ops
     rng = np.random.default_rng(21)
@@ -507,7 +508,8 @@ def test_gemm_decode_shortconv(M, d, L):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("M,F,K", [(3, 256, 64), (16, 640, 96), (64, 384, 128), (200, 256, 80), (2048, 5632, 256), (129, 128, 64)])
+@pytest.mark.parametrize("M,F,K", [(3, 256, 64), (16, 640, 96), (64, 384, 128), (200, 256, 80), (2048, 5632, 256), (129, 128, 64),
+                                   (300, 8192, 128)])
 def test_linear_swiglu_blocked_layout(dtype, M, F, K):
     """Gate and up stacked in blocks of 128 rows: the few-token product, the tensor-core product with
     the activation in its epilogue (more than 128 tokens) and the unfused path all give silu(g) * u."""
